@@ -101,9 +101,11 @@ def default_registry() -> ArchitectureRegistry:
         from ..models.qwen3 import ARCHITECTURE
         from ..models.sufolix import ARCHITECTURE as SUFOLIX
         from ..models.mamevik import ARCHITECTURE as MAMEVIK
+        from ..models.dalavik import ARCHITECTURE as DALAVIK
         _DEFAULT.register(ARCHITECTURE)
         _DEFAULT.register(SUFOLIX)
         _DEFAULT.register(MAMEVIK)
+        _DEFAULT.register(DALAVIK)
     return _DEFAULT
 
 

@@ -43,6 +43,8 @@ MODULES: Dict[str, List[str]] = {
     "moe_gemm_tcgen05": [],
     "ssm": [],
     "latent": [],
+    "sublayer_norm": [],
+    "attention_mix": [],
 }
 
 _LOCK = threading.Lock()

@@ -150,9 +150,12 @@ __device__ __forceinline__ float sigmoid_stable(float x) {
   return e / (1.0f + e);
 }
 
+// What the gate passes through before it multiplies the other half: 0 silu, 1 relu.
+__device__ __forceinline__ float gate_act(float g, int act) { return act == 1 ? fmaxf(g, 0.f) : g * sigmoid_stable(g); }
+
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate, const T* __restrict__ up,
-                                T* __restrict__ out, int rows, int width, int in_stride) {
+                                T* __restrict__ out, int rows, int width, int in_stride, int act) {
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();
   const size_t n = (size_t)rows * width;
@@ -161,13 +164,13 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate, const T* __restrict_
     const int r = (int)(i / width), c = (int)(i % width);
     const float g = to_float(gate[(size_t)r * in_stride + c]);
     const float u = to_float(up[(size_t)r * in_stride + c]);
-    out[i] = from_float<T>(g * sigmoid_stable(g) * u);
+    out[i] = from_float<T>(gate_act(g, act) * u);
   }
 }
 
 // Eight bfloat16 elements per thread with 16-byte accesses.
 __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
-                                       __nv_bfloat16* __restrict__ out, int rows, int width8, int in_stride) {
+                                       __nv_bfloat16* __restrict__ out, int rows, int width8, int in_stride, int act) {
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();
   const size_t n = (size_t)rows * width8;
@@ -182,7 +185,7 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate, c
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
-      o2[j] = __floats2bfloat162_rn(g.x * sigmoid_stable(g.x) * u.x, g.y * sigmoid_stable(g.y) * u.y);
+      o2[j] = __floats2bfloat162_rn(gate_act(g.x, act) * u.x, gate_act(g.y, act) * u.y);
     }
     *reinterpret_cast<uint4*>(out + (size_t)r * width8 * 8 + c) = o4;
   }
@@ -190,23 +193,24 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate, c
 
 // gate = in[:, 0:width], up = in[:, width:2*width] of a [rows, in_stride] matrix.
 ILB_EXPORT int ilb_silu_mul(const void* in, void* out, int dtype, int rows, int width,
-                            int in_stride, cudaStream_t stream) {
+                            int in_stride, int act, cudaStream_t stream) {
   ILB_REQUIRE(rows >= 0 && width > 0 && in_stride >= 2 * width, "silu_mul: bad sizes");
+  ILB_REQUIRE(act == 0 || act == 1, "silu_mul: unknown activation %d", act);
   if (rows == 0) return 0;
   const int threads = 256;
   if (dtype == kBF16 && width % 8 == 0 && in_stride % 8 == 0 && ((uintptr_t)in % 16 == 0) && ((uintptr_t)out % 16 == 0)) {
     const size_t n8 = (size_t)rows * (width / 8);
     const int blocks8 = (int)((n8 + threads - 1) / threads < 148 * 16 ? (n8 + threads - 1) / threads : 148 * 16);
     ilb::launch(silu_mul_bf16x8_kernel, dim3(blocks8), dim3(threads), 0, stream, (const __nv_bfloat16*)in,
-                (const __nv_bfloat16*)in + width, (__nv_bfloat16*)out, rows, width / 8, in_stride);
+                (const __nv_bfloat16*)in + width, (__nv_bfloat16*)out, rows, width / 8, in_stride, act);
     return check_launch("silu_mul");
   }
   const size_t n = (size_t)rows * width;
   const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
   if (dtype == kF32)
-    ilb::launch(silu_mul_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)in, (const float*)in + width, (float*)out, rows, width, in_stride);
+    ilb::launch(silu_mul_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)in, (const float*)in + width, (float*)out, rows, width, in_stride, act);
   else if (dtype == kBF16)
-    ilb::launch(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)in, (const __nv_bfloat16*)in + width, (__nv_bfloat16*)out, rows, width, in_stride);
+    ilb::launch(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)in, (const __nv_bfloat16*)in + width, (__nv_bfloat16*)out, rows, width, in_stride, act);
   else
     return fail("silu_mul: unknown dtype %d", dtype);
   return check_launch("silu_mul");

@@ -8,6 +8,13 @@
 //
 //   latent_write   c = x / sqrt(mean(x^2) + eps) * g in 32-bit from the projection's columns, stored
 //                  into the token's place of its page (dummy rows and released pages are skipped)
+//
+// A layer may keep a ROTATED KEY PART beside the latent: `tail` more columns of the projection, shared by all
+// heads, turned by the token's position in pairs of neighbours (the first `rot` of them; the rest pass) and stored
+// behind the latent in the same cache row (row = rank + tail).  Every head's query then ends in `tail` columns of
+// its own that are turned the same way and copied behind the head's mapped query, so that one dot product over
+// rank + tail elements gives q_a . k_a + q_r . k_r.  The same launch does both; a layer that reads another layer's
+// cache runs it for its queries alone (cache null).
 //   head_matmul    out[t, i, :] = x[t, i, :] W[i] for every head i, W [heads, K, N]: the two maps
 //                  above, 16 tokens a block so that a head's matrix is read once per 16 tokens;
 //                  32-bit sums (a step of at most 16 tokens cuts k in four parts that are added in order)
@@ -21,13 +28,53 @@ struct LatentWrite {
   const float* w; float eps;
   const int* positions; const int* seq_of_token; const int* block_table;
   int col0, rank, max_blocks, page_size, num_pages;
+  // the rotated part (tail 0: none): cos/sin per token [tokens][rot / 2][2]
+  int tail, rot;
+  const float* angles;
 };
 
-// One block of 128 threads writes the latent of token t.
-template <typename TI, typename TC>
+// The queries' tails of token t: head i's columns [qcol0 + i * qhs, + tail) of `qsrc` turned into columns
+// [rank + i * (rank + tail), + tail) of `qdst`.
+struct QueryTails {
+  const void* src; void* dst;
+  int ld_src, ld_dst, heads, col0, head_stride;
+};
+
+template <typename T>
+__device__ __forceinline__ void turn_pair(const T* __restrict__ src, int i, int tail, int rot, const float* __restrict__ cs,
+                                          float& a, float& b) {
+  // elements 2i and 2i + 1 (b unused when 2i + 1 == tail)
+  const float u = to_float(src[2 * i]);
+  const float v = 2 * i + 1 < tail ? to_float(src[2 * i + 1]) : 0.f;
+  if (2 * i + 1 < rot) {
+    const float c = cs[2 * i], s = cs[2 * i + 1];
+    a = u * c - v * s;
+    b = v * c + u * s;
+  } else {
+    a = u; b = v;
+  }
+}
+
+// One block of 128 threads writes the latent (and the rotated part) of token t, and turns its queries' tails.
+template <typename TI, typename TC, typename TQ = TI>
 __device__ __forceinline__ void latent_write_token(const TI* __restrict__ proj, int ld, const LatentWrite& a, TC* __restrict__ cache,
-                                                   int t, float* scratch) {
+                                                   int t, float* scratch, const QueryTails* qt = nullptr) {
   const int col0 = a.col0, rank = a.rank, max_blocks = a.max_blocks, page_size = a.page_size, num_pages = a.num_pages;
+  const int tail = a.tail, rot = a.rot, pairs = (tail + 1) / 2;
+  const float* cs = a.angles != nullptr ? a.angles + (size_t)t * rot : nullptr;
+  if (qt != nullptr && tail > 0) {
+    const TQ* qsrc = reinterpret_cast<const TQ*>(qt->src) + (size_t)t * qt->ld_src + qt->col0;
+    TQ* qdst = reinterpret_cast<TQ*>(qt->dst) + (size_t)t * qt->ld_dst + rank;
+    for (int e = threadIdx.x; e < qt->heads * pairs; e += blockDim.x) {
+      const int h = e / pairs, i = e % pairs;
+      float u, v;
+      turn_pair<TQ>(qsrc + (size_t)h * qt->head_stride, i, tail, rot, cs, u, v);
+      TQ* o = qdst + (size_t)h * (rank + tail);
+      o[2 * i] = from_float<TQ>(u);
+      if (2 * i + 1 < tail) o[2 * i + 1] = from_float<TQ>(v);
+    }
+  }
+  if (cache == nullptr) return;
   const float* w = a.w;
   const float eps = a.eps;
   const int* positions = a.positions;
@@ -44,9 +91,15 @@ __device__ __forceinline__ void latent_write_token(const TI* __restrict__ proj, 
   const int pos = positions[t];
   const int page = block_table[(size_t)seq_of_token[t] * max_blocks + pos / page_size];
   if (page < 0 || page >= num_pages) return;
-  TC* dst = cache + ((size_t)page * page_size + pos % page_size) * rank;
+  TC* dst = cache + ((size_t)page * page_size + pos % page_size) * (rank + tail);
   for (int i = threadIdx.x; i < rank; i += blockDim.x)
     dst[i] = from_float<TC>(to_float(row[i]) * inv * w[i]);
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    float u, v;
+    turn_pair<TI>(row + rank, i, tail, rot, cs, u, v);
+    dst[rank + 2 * i] = from_float<TC>(u);
+    if (2 * i + 1 < tail) dst[rank + 2 * i + 1] = from_float<TC>(v);
+  }
 }
 
 template <typename TI, typename TC>
@@ -64,7 +117,7 @@ ILB_EXPORT int ilb_latent_write(const void* proj, int dtype, int ld, int col0, i
   ILB_REQUIRE(rank > 0 && ld >= col0 + rank && n_tokens >= 0 && eps > 0.f, "latent_write: bad sizes");
   ILB_REQUIRE(page_size > 0 && max_blocks > 0 && num_pages > 0, "latent_write: bad cache geometry");
   if (n_tokens == 0) return 0;
-  const LatentWrite a{w, eps, positions, seq_of_token, block_table, col0, rank, max_blocks, page_size, num_pages};
+  const LatentWrite a{w, eps, positions, seq_of_token, block_table, col0, rank, max_blocks, page_size, num_pages, 0, 0, nullptr};
 #define ILB_LW(TI, TC) ilb::launch(latent_write_kernel<TI, TC>, dim3(n_tokens), dim3(128), 0, stream, (const TI*)proj, ld, a, (TC*)cache)
   if (dtype == kF32 && cache_dtype == kF32) ILB_LW(float, float);
   else if (dtype == kBF16 && cache_dtype == kBF16) ILB_LW(__nv_bfloat16, __nv_bfloat16);
@@ -75,18 +128,56 @@ ILB_EXPORT int ilb_latent_write(const void* proj, int dtype, int ld, int col0, i
   return check_launch("latent_write");
 }
 
+// The latent with a rotated part behind it, and the queries' tails, of every token of a step (see the top).
+template <typename TI, typename TC, typename TQ>
+__global__ void __launch_bounds__(128)
+latent_write_rot_kernel(const TI* __restrict__ proj, int ld, const LatentWrite a, TC* __restrict__ cache, const QueryTails qt) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  __shared__ float scratch[33];
+  latent_write_token<TI, TC, TQ>(proj, ld, a, cache, blockIdx.x, scratch, qt.src != nullptr ? &qt : nullptr);
+}
+
+// proj [T, ld] (`dtype`): the latent's columns from col0, the part to rotate right behind them; cache rows of
+// rank + tail elements (null: nothing is stored); angles [T, rot / 2, 2] (cos, sin); q_src [T, ld_q] (`q_dtype`), head i's
+// tail at columns q_col0 + i * q_head_stride; q_dst [T, heads * (rank + tail)].
+ILB_EXPORT int ilb_latent_write_rot(const void* proj, int dtype, int ld, int col0, int rank, int tail, int rot, const float* angles,
+                                    const float* w, float eps, const int* positions, const int* seq_of_token, const int* block_table,
+                                    int max_blocks, int page_size, int num_pages, void* cache, int cache_dtype, const void* q_src,
+                                    void* q_dst, int q_dtype, int ld_q, int q_col0, int q_head_stride, int heads, int n_tokens,
+                                    cudaStream_t stream) {
+  ILB_REQUIRE(rank > 0 && tail >= 0 && n_tokens >= 0, "latent_write_rot: bad sizes");
+  ILB_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= tail && (rot == 0 || angles != nullptr), "latent_write_rot: %d of %d elements cannot turn in pairs", rot, tail);
+  ILB_REQUIRE(cache == nullptr || (ld >= col0 + rank + tail && eps > 0.f && w != nullptr && page_size > 0 && max_blocks > 0 && num_pages > 0),
+              "latent_write_rot: bad cache geometry");
+  ILB_REQUIRE(q_src == nullptr || (q_dst != nullptr && heads > 0 && q_head_stride >= tail && ld_q >= q_col0 + (heads - 1) * q_head_stride + tail),
+              "latent_write_rot: the queries' rows are too short");
+  ILB_REQUIRE(cache != nullptr || q_src != nullptr, "latent_write_rot: nothing to do");
+  if (n_tokens == 0) return 0;
+  const LatentWrite a{w, eps, positions, seq_of_token, block_table, col0, rank, max_blocks, page_size, num_pages, tail, rot, angles};
+  const QueryTails qt{q_src, q_dst, ld_q, heads * (rank + tail), heads, q_col0, q_head_stride};
+#define ILB_LW(TI, TC, TQ) ilb::launch(latent_write_rot_kernel<TI, TC, TQ>, dim3(n_tokens), dim3(128), 0, stream, (const TI*)proj, ld, a, (TC*)cache, qt)
+  const int cd = cache != nullptr ? cache_dtype : q_dtype;
+  if (dtype == kF32 && cd == kF32 && q_dtype == kF32) ILB_LW(float, float, float);
+  else if (dtype == kF32 && cd == kBF16 && q_dtype == kBF16) ILB_LW(float, __nv_bfloat16, __nv_bfloat16);
+  else if (dtype == kBF16 && cd == kBF16 && q_dtype == kBF16) ILB_LW(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+  else return fail("latent_write_rot: unsupported dtypes %d/%d/%d", dtype, cd, q_dtype);
+#undef ILB_LW
+  return check_launch("latent_write_rot");
+}
+
 constexpr int kHeadTokens = 16;
 
 // Block (128 / KS columns n) x (KS ranges of k).  Many tokens: KS = 1, a thread owns a column for 16 tokens.  A step
 // of few tokens has few blocks of that kind, so its k range is cut in four and the parts meet in shared memory.
 template <typename TI, typename TW, typename TO, int KS>
 __device__ __forceinline__ void head_matmul_block(const TI* __restrict__ x, int ldx, const TW* __restrict__ w, TO* __restrict__ out,
-                                                  int ldo, int n_tokens, int K, int N, int t0, int h, int n_block, float* xs) {
+                                                  int ldo, int n_tokens, int K, int N, int xhs, int ohs, int t0, int h, int n_block, float* xs) {
   constexpr int NT = 128 / KS;
   const int ts = min(kHeadTokens, n_tokens - t0);
   for (int i = threadIdx.x; i < kHeadTokens * K; i += 128) {
     const int tt = i / K, k = i % K;
-    xs[i] = tt < ts ? to_float(x[(size_t)(t0 + tt) * ldx + (size_t)h * K + k]) : 0.f;
+    xs[i] = tt < ts ? to_float(x[(size_t)(t0 + tt) * ldx + (size_t)h * xhs + k]) : 0.f;
   }
   __syncthreads();
   const int tn = threadIdx.x % NT, tk = threadIdx.x / NT;
@@ -132,17 +223,17 @@ __device__ __forceinline__ void head_matmul_block(const TI* __restrict__ x, int 
   if (!live) return;
 #pragma unroll
   for (int tt = 0; tt < kHeadTokens; ++tt)
-    if (tt < ts) out[(size_t)(t0 + tt) * ldo + (size_t)h * N + n] = from_float<TO>(acc[tt]);
+    if (tt < ts) out[(size_t)(t0 + tt) * ldo + (size_t)h * ohs + n] = from_float<TO>(acc[tt]);
 }
 
 template <typename TI, typename TW, typename TO, int KS>
 __global__ void __launch_bounds__(128)
 head_matmul_kernel(const TI* __restrict__ x, int ldx, const TW* __restrict__ w, TO* __restrict__ out, int ldo,
-                   int n_tokens, int K, int N) {
+                   int n_tokens, int K, int N, int xhs, int ohs) {
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();
   extern __shared__ __align__(16) float xs[];           // [kHeadTokens][K], then (KS > 1) [KS][kHeadTokens][NT]
-  head_matmul_block<TI, TW, TO, KS>(x, ldx, w, out, ldo, n_tokens, K, N, blockIdx.x * kHeadTokens, blockIdx.y, blockIdx.z, xs);
+  head_matmul_block<TI, TW, TO, KS>(x, ldx, w, out, ldo, n_tokens, K, N, xhs, ohs, blockIdx.x * kHeadTokens, blockIdx.y, blockIdx.z, xs);
 }
 
 // The input stage of a step of few tokens in one launch: blocks (tile of 16 tokens, head, 32 columns) map the queries
@@ -158,7 +249,7 @@ latent_input_kernel(const TI* __restrict__ proj, int ld, const TI* __restrict__ 
   const int n_blocks = (N + 31) / 32, t0 = blockIdx.x * kHeadTokens;
   const int y = blockIdx.y;
   if (y < heads * n_blocks) {
-    head_matmul_block<TI, TI, TO, 4>(proj, ld, w, q_out, ldo, n_tokens, K, N, t0, y / n_blocks, y % n_blocks, xs);
+    head_matmul_block<TI, TI, TO, 4>(proj, ld, w, q_out, ldo, n_tokens, K, N, K, N, t0, y / n_blocks, y % n_blocks, xs);
   } else {
     const int t = t0 + (y - heads * n_blocks);
     if (t < n_tokens) latent_write_token<TI, TC>(proj, ld, a, cache, t, scratch);
@@ -173,7 +264,7 @@ constexpr int kMmaTile = 64;
 
 __global__ void __launch_bounds__(128)
 head_matmul_mma_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ w,
-                       __nv_bfloat16* __restrict__ out, int ldo, int n_tokens, int K, int N) {
+                       __nv_bfloat16* __restrict__ out, int ldo, int n_tokens, int K, int N, int xhs, int ohs) {
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();
   __shared__ __align__(16) __nv_bfloat16 ws[kMmaTile][kMmaTile + 8];
@@ -181,8 +272,8 @@ head_matmul_mma_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int r0 = t0 + warp * 16 + g, r1 = r0 + 8;
   const bool live0 = r0 < n_tokens, live1 = r1 < n_tokens;
-  const __nv_bfloat16* a0 = x + (size_t)(live0 ? r0 : 0) * ldx + (size_t)h * K;
-  const __nv_bfloat16* a1 = x + (size_t)(live1 ? r1 : 0) * ldx + (size_t)h * K;
+  const __nv_bfloat16* a0 = x + (size_t)(live0 ? r0 : 0) * ldx + (size_t)h * xhs;
+  const __nv_bfloat16* a1 = x + (size_t)(live1 ? r1 : 0) * ldx + (size_t)h * xhs;
   float acc[kMmaTile / 8][4];
 #pragma unroll
   for (int i = 0; i < kMmaTile / 8; ++i)
@@ -221,22 +312,23 @@ head_matmul_mma_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_
   for (int i = 0; i < kMmaTile / 8; ++i) {
     const int col = n0 + i * 8 + 2 * t;
     if (col >= N) continue;
-    if (live0) *reinterpret_cast<uint32_t*>(out + (size_t)r0 * ldo + (size_t)h * N + col) = pack_bf16(acc[i][0], acc[i][1]);
-    if (live1) *reinterpret_cast<uint32_t*>(out + (size_t)r1 * ldo + (size_t)h * N + col) = pack_bf16(acc[i][2], acc[i][3]);
+    if (live0) *reinterpret_cast<uint32_t*>(out + (size_t)r0 * ldo + (size_t)h * ohs + col) = pack_bf16(acc[i][0], acc[i][1]);
+    if (live1) *reinterpret_cast<uint32_t*>(out + (size_t)r1 * ldo + (size_t)h * ohs + col) = pack_bf16(acc[i][2], acc[i][3]);
   }
 }
 
-// x: [T, ldx] of `dtype`, head i at columns i * K ..; w: [heads, K, N] of `dtype`; out: [T, ldo] of
-// `out_dtype`, head i at columns i * N ...
+// x: [T, ldx] of `dtype`, head i at columns i * xhs ..; w: [heads, K, N] of `dtype`; out: [T, ldo] of
+// `out_dtype`, head i at columns i * ohs ... (xhs >= K and ohs >= N: a head's row may hold more than the product reads or writes)
 ILB_EXPORT int ilb_head_matmul(const void* x, int dtype, int ldx, const void* w, void* out, int out_dtype, int ldo,
-                               int n_tokens, int heads, int K, int N, cudaStream_t stream) {
+                               int n_tokens, int heads, int K, int N, int xhs, int ohs, cudaStream_t stream) {
   ILB_REQUIRE(n_tokens >= 0 && heads > 0 && heads <= 65535 && K > 0 && N > 0, "head_matmul: bad sizes");
-  ILB_REQUIRE(ldx >= heads * K && ldo >= heads * N, "head_matmul: strides too small");
+  ILB_REQUIRE(xhs >= K && ohs >= N && ldx >= (heads - 1) * xhs + K && ldo >= (heads - 1) * ohs + N, "head_matmul: strides too small");
   if (dtype == kBF16 && out_dtype == kBF16 && n_tokens > kHeadTokens && K % 16 == 0 && N % 8 == 0 && ldx % 2 == 0 && ldo % 2 == 0 &&
+      xhs % 2 == 0 && ohs % 2 == 0 &&
       ((uintptr_t)x % 4 == 0) && ((uintptr_t)out % 4 == 0) && ((uintptr_t)w % 16 == 0)) {
     const dim3 grid((n_tokens + kMmaTile - 1) / kMmaTile, heads, (N + kMmaTile - 1) / kMmaTile);
     ilb::launch(head_matmul_mma_kernel, grid, dim3(128), 0, stream, (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w,
-                (__nv_bfloat16*)out, ldo, n_tokens, K, N);
+                (__nv_bfloat16*)out, ldo, n_tokens, K, N, xhs, ohs);
     return check_launch("head_matmul");
   }
   const bool few = n_tokens <= kHeadTokens;
@@ -248,9 +340,9 @@ ILB_EXPORT int ilb_head_matmul(const void* x, int dtype, int ldx, const void* w,
 #define ILB_HM(TI, TO)                                                                                                        \
   do {                                                                                                                        \
     if (few) ilb::launch(head_matmul_kernel<TI, TI, TO, 4>, grid, dim3(128), smem, stream, (const TI*)x, ldx, (const TI*)w,   \
-                         (TO*)out, ldo, n_tokens, K, N);                                                                      \
+                         (TO*)out, ldo, n_tokens, K, N, xhs, ohs);                                                            \
     else ilb::launch(head_matmul_kernel<TI, TI, TO, 1>, grid, dim3(128), smem, stream, (const TI*)x, ldx, (const TI*)w,       \
-                     (TO*)out, ldo, n_tokens, K, N);                                                                          \
+                     (TO*)out, ldo, n_tokens, K, N, xhs, ohs);                                                                \
   } while (0)
   if (dtype == kF32 && out_dtype == kF32) ILB_HM(float, float);
   else if (dtype == kBF16 && out_dtype == kBF16) ILB_HM(__nv_bfloat16, __nv_bfloat16);
@@ -273,7 +365,7 @@ ILB_EXPORT int ilb_latent_input(const void* proj, int dtype, int ld, const void*
   const long long rows = (long long)heads * ((N + 31) / 32) + kHeadTokens;
   ILB_REQUIRE(rows <= 65535, "latent_input: too many heads");
   if (n_tokens == 0) return 0;
-  const LatentWrite a{norm_w, eps, positions, seq_of_token, block_table, col0, rank, max_blocks, page_size, num_pages};
+  const LatentWrite a{norm_w, eps, positions, seq_of_token, block_table, col0, rank, max_blocks, page_size, num_pages, 0, 0, nullptr};
   const dim3 grid((n_tokens + kHeadTokens - 1) / kHeadTokens, (unsigned)rows);
 #define ILB_LI(TI, TC, TO) ilb::launch(latent_input_kernel<TI, TC, TO>, grid, dim3(128), smem, stream, (const TI*)proj, ld, (const TI*)w, \
                                         (TO*)q_out, ldo, n_tokens, heads, K, N, a, (TC*)cache)

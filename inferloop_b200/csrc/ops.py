@@ -115,14 +115,17 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
           _i(rows), _i(width), _f(eps), _stream(x))
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out = silu(gate_up[:, :I]) * gate_up[:, I:2I]."""
+GATE_ACTIVATIONS = {"silu": 0, "relu": 1}
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
+    """out = act(gate_up[:, :I]) * gate_up[:, I:2I], act = silu (default) or relu."""
     _need(gate_up, "silu_mul in"); _need(out, "silu_mul out", gate_up.dtype)
     rows, width = out.shape
     if gate_up.shape[0] != rows or gate_up.shape[1] != 2 * width:
         raise KernelError("silu_mul: shapes do not agree")
     _call("elementwise", "ilb_silu_mul", _ptr(gate_up), _ptr(out), _i(_code(out)), _i(rows),
-          _i(width), _i(gate_up.shape[1]), _stream(out))
+          _i(width), _i(gate_up.shape[1]), _i(GATE_ACTIVATIONS[activation]), _stream(out))
 
 
 def glu_mul(gate_up: torch.Tensor, out: torch.Tensor, limit: float = 0.0, sharpness: float = 1.0, up_offset: float = 0.0) -> None:
@@ -272,15 +275,82 @@ def latent_input(proj: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, col0:
           _i(_code(cache)), _stream(cache))
 
 
-def head_matmul(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, i, :] = x[t, i, :] @ w[i] for every head i; x [T, >= heads * K] (row stride free), w [heads, K, N],
-    out [T, heads * N]."""
-    _need(x, "head_matmul x", contiguous=False); _need(w, "head_matmul w", x.dtype); _need(out, "head_matmul out")
+def head_matmul(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, x_head_stride: Optional[int] = None,
+                out_head_stride: Optional[int] = None) -> None:
+    """out[t, i, :N] = x[t, i, :K] @ w[i] for every head i; w [heads, K, N]; head i of x starts at column
+    i * x_head_stride (default K), head i of out at i * out_head_stride (default N); row strides are free."""
+    _need(x, "head_matmul x", contiguous=False); _need(w, "head_matmul w", x.dtype); _need(out, "head_matmul out", contiguous=False)
     heads, K, N = w.shape
-    if x.stride(1) != 1 or x.shape[1] < heads * K or tuple(out.shape) != (x.shape[0], heads * N):
+    xhs = K if x_head_stride is None else int(x_head_stride)
+    ohs = N if out_head_stride is None else int(out_head_stride)
+    if (x.stride(1) != 1 or out.stride(1) != 1 or xhs < K or ohs < N or x.shape[1] < (heads - 1) * xhs + K
+            or out.shape[0] != x.shape[0] or out.shape[1] < (heads - 1) * ohs + N):
         raise KernelError("head_matmul: shapes do not agree")
     _call("latent", "ilb_head_matmul", _ptr(x), _i(_code(x)), _i(x.stride(0)), _ptr(w), _ptr(out), _i(_code(out)), _i(out.stride(0)),
-          _i(x.shape[0]), _i(heads), _i(K), _i(N), _stream(out))
+          _i(x.shape[0]), _i(heads), _i(K), _i(N), _i(xhs), _i(ohs), _stream(out))
+
+
+def latent_write_rot(proj: torch.Tensor, col0: int, rank: int, tail: int, rot: int, angles: Optional[torch.Tensor],
+                     weight: Optional[torch.Tensor], eps: float, step, block_table: Optional[torch.Tensor],
+                     cache: Optional[torch.Tensor], q_src: Optional[torch.Tensor] = None, q_dst: Optional[torch.Tensor] = None,
+                     q_col0: int = 0, q_head_stride: int = 0, heads: int = 0) -> None:
+    """A latent with a rotated part behind it: cache row of token t = [rms(proj[t, col0 : col0 + rank]) * weight |
+    turn(proj[t, col0 + rank : + tail])], the first `rot` elements of the part turned in neighbouring pairs by
+    `angles` [T, rot / 2, 2] (cos, sin); cache is [pages, 1, page_size, rank + tail] (None: nothing stored).  With
+    `q_src` [T, >= q_col0 + heads * q_head_stride]: head i's `tail` columns from q_col0 + i * q_head_stride are
+    turned the same way into q_dst[t, i, rank:], q_dst [T, heads * (rank + tail)]."""
+    _need(proj, "latent projection", contiguous=False); _need(weight, "latent norm weight", torch.float32); _need(cache, "latent cache")
+    _need(block_table, "block table", torch.int32); _need(angles, "rotation table", torch.float32)
+    _need(q_src, "queries", contiguous=False); _need(q_dst, "mapped queries", None if q_src is None else q_src.dtype)
+    T = step.n_tokens
+    if cache is not None and (cache.dim() != 4 or cache.shape[1] != 1 or cache.shape[3] != rank + tail or weight is None
+                              or weight.numel() != rank or block_table is None):
+        raise KernelError("latent_write_rot: cache must be [pages, 1, page_size, rank + tail]")
+    if proj.shape[0] != T or (angles is not None and tuple(angles.shape) != (T, rot // 2, 2)):
+        raise KernelError("latent_write_rot: rows do not match the step")
+    if q_src is not None and (q_dst is None or q_src.shape[0] != T or tuple(q_dst.shape) != (T, heads * (rank + tail))):
+        raise KernelError("latent_write_rot: the queries do not match the step")
+    ref = cache if cache is not None else q_dst
+    _call("latent", "ilb_latent_write_rot", _ptr(proj), _i(_code(proj)), _i(proj.stride(0)), _i(col0), _i(rank), _i(tail), _i(rot),
+          _ptr(angles), _ptr(weight), _f(eps), _ptr(step.positions), _ptr(step.seq_of_token), _ptr(block_table),
+          _i(0 if block_table is None else block_table.shape[1]), _i(0 if cache is None else cache.shape[2]),
+          _i(0 if cache is None else cache.shape[0]), _ptr(cache), _i(_code(ref)), _ptr(q_src), _ptr(q_dst),
+          _i(_code(ref if q_src is None else q_src)), _i(0 if q_src is None else q_src.stride(0)), _i(q_col0), _i(q_head_stride),
+          _i(heads), _i(T), _stream(ref))
+
+
+# --------------------------------------------------------------------------- norm on a sublayer's output
+def cast_zero(x: torch.Tensor, xc: torch.Tensor, y: torch.Tensor) -> None:
+    """xc = x in xc's dtype; y = 0 (x and y 32-bit, all of one shape)."""
+    _need(x, "cast_zero x", torch.float32); _need(xc, "cast_zero out"); _need(y, "cast_zero y", torch.float32)
+    if xc.shape != x.shape or y.shape != x.shape:
+        raise KernelError("cast_zero: shapes do not agree")
+    _call("sublayer_norm", "ilb_cast_zero", _ptr(x), _ptr(xc), _i(_code(xc)), _ptr(y), ctypes.c_longlong(x.numel()), _stream(x))
+
+
+def group_norm_add(y: torch.Tensor, weight: torch.Tensor, eps: float, groups: int, x: Optional[torch.Tensor] = None,
+                   out: Optional[torch.Tensor] = None, zero: bool = False) -> None:
+    """n = y cut into `groups` equal consecutive parts, each divided by sqrt(mean(part^2) + eps), times weight.
+    With `x`: x += n and out (if given) = the new x; without: out = n.  `zero` leaves y at zero.  y [rows, width]
+    32-bit with a free row stride."""
+    _need(y, "group_norm y", torch.float32, contiguous=False); _need(weight, "group_norm weight", torch.float32)
+    _need(x, "group_norm x", torch.float32); _need(out, "group_norm out")
+    rows, width = y.shape
+    if y.stride(1) != 1 or weight.numel() != width or (x is not None and x.shape != y.shape) or (out is not None and out.shape != y.shape):
+        raise KernelError("group_norm_add: shapes do not agree")
+    _call("sublayer_norm", "ilb_group_norm_add", _ptr(y), _i(y.stride(0)), _ptr(weight), _f(eps), _i(groups), _i(rows), _i(width),
+          _ptr(x), _ptr(out), _i(F32 if out is None else _code(out)), _i(1 if zero else 0), _stream(y))
+
+
+def gated_rows(a: torch.Tensor, table: torch.Tensor, col0: int, tokens: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, k] = gelu_tanh(a[t, k]) * table[tokens[t], col0 + k]."""
+    _need(a, "gated_rows a"); _need(table, "gated_rows table", a.dtype); _need(out, "gated_rows out", a.dtype)
+    _need(tokens, "gated_rows tokens", torch.int32)
+    rows, width = a.shape
+    if out.shape != a.shape or tokens.numel() != rows or table.shape[1] < col0 + width:
+        raise KernelError("gated_rows: shapes do not agree")
+    _call("sublayer_norm", "ilb_gated_rows", _ptr(a), _ptr(table), _i(_code(a)), _i(table.stride(0)), _i(col0), _ptr(tokens),
+          _i(table.shape[0]), _ptr(out), _i(rows), _i(width), _stream(out))
 
 
 def gather_rows(x: torch.Tensor, index: torch.Tensor, out: torch.Tensor, streams: int = 1) -> None:
@@ -569,6 +639,28 @@ def paged_attention_simple(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Te
           _ptr(block_table), _i(block_table.shape[1]), _i(page_size), _i(num_pages),
           _i(window or 0), _f(scale), _i(q.shape[0]), _i(nq), _i(nkv), _i(d), _i(dv), _i(q.shape[1]),
           _i(out.shape[1]), _ptr(sink), _stream(q))
+
+
+def attention_mixed_heads(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, step,
+                          block_table: torch.Tensor, window: int, scale: float, nq: int, nkv: int, d: int, dv: int,
+                          sink: Optional[torch.Tensor] = None, head_mix: Optional[torch.Tensor] = None,
+                          dist_r1: Optional[torch.Tensor] = None, dist_r2: Optional[torch.Tensor] = None,
+                          softcap: float = 0.0, temp_coef: float = 0.0, temp_every: int = 1) -> None:
+    """Causal attention whose scores are capped, shifted by a distance term and mixed across heads before the
+    softmax (see attention_mix.cu): s = scale * (1 + temp_coef ln(floor((i + 1) / temp_every) + 1)) q.k;
+    s <- softcap tanh(s / softcap); s <- s - r1 ln(1 + r2 (i - j)); z_h = sum_g head_mix[h, g] s_g; softmax with `sink`."""
+    _need(q, "attention q"); _need(out, "attention out", q.dtype); _need(k_cache, "k cache"); _need(v_cache, "v cache", k_cache.dtype)
+    for t, what, n in ((sink, "sink", nq), (head_mix, "head mixing matrix", nq * nq), (dist_r1, "distance r1", nq), (dist_r2, "distance r2", nq)):
+        _need(t, "attention " + what, torch.float32)
+        if t is not None and t.numel() != n:
+            raise KernelError(f"attention: the {what} has {t.numel()} elements, {n} are needed")
+    num_pages, nkv_c, page_size, d_c = k_cache.shape
+    if (nkv_c, d_c) != (nkv, d) or tuple(v_cache.shape) != (num_pages, nkv, page_size, dv):
+        raise KernelError("attention: cache shape does not match the heads")
+    _call("attention_mix", "ilb_attention_mix", _ptr(q), _ptr(out), _i(_code(q)), _ptr(k_cache), _ptr(v_cache), _i(_code(k_cache)),
+          _ptr(step.positions), _ptr(step.seq_of_token), _ptr(block_table), _i(block_table.shape[1]), _i(page_size), _i(num_pages),
+          _i(window or 0), _f(scale), _i(q.shape[0]), _i(nq), _i(nkv), _i(d), _i(dv), _i(q.shape[1]), _i(out.shape[1]),
+          _ptr(sink), _ptr(head_mix), _ptr(dist_r1), _ptr(dist_r2), _f(softcap), _f(temp_coef), _i(temp_every), _stream(q))
 
 
 # --------------------------------------------------------------------------- sampling

@@ -44,11 +44,18 @@ class DecoderModel:
         out += self.final_norm.declare_weights()
         if s.head_name is not None:
             out.append(WeightDecl(s.head_name, (s.vocab_size, s.hidden_size), root=True))
-        names = [d.name for d in out]
-        if len(set(names)) != len(names):
-            dup = sorted({n for n in names if names.count(n) > 1})
-            raise ValueError(f"tensor names declared twice: {dup}")
-        return out
+        # Parts may share a tensor of the model (every layer reading its slice of one table): equal
+        # declarations count once; the same name declared otherwise is a fault.
+        seen, unique, dup = {}, [], set()
+        for d in out:
+            if d.name not in seen:
+                seen[d.name] = d
+                unique.append(d)
+            elif seen[d.name] != d:
+                dup.add(d.name)
+        if dup:
+            raise ValueError(f"tensor names declared twice: {sorted(dup)}")
+        return unique
 
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         s = self.spec

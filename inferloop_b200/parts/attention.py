@@ -21,6 +21,13 @@ False / "qkv" (no bias on the output projection), `qk_norm` = True (weight [head
 (`names`: pairs (role, name under the prefix)), and `value_mix` = "first" | "mixed": the first
 such layer of a model keeps its values of the step's tokens, every later one caches
 (1 - lambda) v + lambda v_first with its own learned scalar lambda.
+
+Scores may be reshaped and mixed across heads before the softmax (each a spec parameter, absent by
+default; any of them sends the layer to the kernel that owns a token with all its heads,
+csrc/attention_mix.cu): `query_temperature` = (coef, every): q at position i is multiplied by
+1 + coef ln(floor((i + 1) / every) + 1); `softcap` = c: s <- c tanh(s / c); `distance_bias`: s <- s -
+r1_h ln(1 + r2_h (i - j)) with two learned vectors; `head_mix`: s_h <- sum_g M[h, g] s_g with a learned
+[heads, heads] matrix; in that order.  `sink`: a learned logit per head joins the softmax's denominator.
 """
 from __future__ import annotations
 
@@ -71,12 +78,24 @@ class GQAttention(Mixer):
         # split-KV decode cuts the keys at multiples of this, fixed per model so that the
         # cut never depends on the batch
         self.decode_chunk = ops.decode_chunk_for(int(spec.get("max_positions", 4096)))
+        temp = spec.get("query_temperature")
+        self.temp_coef, self.temp_every = (float(temp[0]), int(temp[1])) if temp else (0.0, 1)
+        if temp and self.temp_every <= 0:
+            raise ValueError("query_temperature: the period must be positive")
+        self.softcap = float(spec.get("softcap") or 0.0)
+        self.distance_bias = bool(spec.get("distance_bias", False))
+        self.head_mix = bool(spec.get("head_mix", False))
+        self.has_sink = bool(spec.get("sink", False))
+        self.shaped = bool(self.temp_coef or self.softcap or self.distance_bias or self.head_mix)
+        if self.shaped and self.value_mix is not None:
+            raise ValueError("attention: reshaped scores and mixed values are not served together")
         self.position = registry.build("position", spec["position"], ctx)
         self.rotary_dim = int(spec["position"].get("rotary_dim", 0))
         p = prefix
         names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
                  "qb": "q_proj.bias", "kb": "k_proj.bias", "vb": "v_proj.bias", "ob": "o_proj.bias",
-                 "qn": "q_norm.weight", "kn": "k_norm.weight", "vmix": "v_mix"}
+                 "qn": "q_norm.weight", "kn": "k_norm.weight", "vmix": "v_mix",
+                 "r1": "r1", "r2": "r2", "head_mix": "talk", "sink": "sink"}
         for role, name in spec.get("names", ()):
             if role not in names:
                 raise ValueError(f"attention has no tensor role {role!r}")
@@ -86,6 +105,7 @@ class GQAttention(Mixer):
                      | (ops.NORM_AFTER_ROTATION if self.qk_norm_after else 0)
                      | (ops.NORM_UNWEIGHTED if self.qk_norm_unweighted else 0))
         self.w_qkv = self.b_qkv = self.w_o = self.b_o = self.q_norm = self.k_norm = self.v_lambda = None
+        self.r1 = self.r2 = self.mix = self.sink = None
 
     # ------------------------------------------------------------------ weights
     def declare_weights(self) -> List[WeightDecl]:
@@ -101,6 +121,12 @@ class GQAttention(Mixer):
         if self.qk_norm:
             out += [WeightDecl(n["qn"], (d,), "vector", "norm"),
                     WeightDecl(n["kn"], (d,), "vector", "norm")]
+        if self.distance_bias:
+            out += [WeightDecl(n["r1"], (self.nq,), "vector", "positive"), WeightDecl(n["r2"], (self.nq,), "vector", "positive")]
+        if self.head_mix:
+            out.append(WeightDecl(n["head_mix"], (self.nq, self.nq), "vector", "eye"))
+        if self.has_sink:
+            out.append(WeightDecl(n["sink"], (self.nq,), "vector", "around_zero"))
         if self.value_mix == "mixed":
             out.append(WeightDecl(n["vmix"], (), "vector", "mix"))
         elif bool(self.spec.get("value_mix_tensor_unused", False)):
@@ -120,6 +146,12 @@ class GQAttention(Mixer):
         if self.qk_norm:
             self.q_norm = tensors[n["qn"]].contiguous()
             self.k_norm = tensors[n["kn"]].contiguous()
+        if self.distance_bias:
+            self.r1, self.r2 = tensors[n["r1"]].contiguous(), tensors[n["r2"]].contiguous()
+        if self.head_mix:
+            self.mix = tensors[n["head_mix"]].contiguous()
+        if self.has_sink:
+            self.sink = tensors[n["sink"]].contiguous()
 
     def cache_needs(self) -> CacheNeeds:
         return CacheNeeds(paged=PagedKVNeed(self.nkv, self.d, self.window, self.dv if self.dv != self.d else None))
@@ -146,6 +178,7 @@ class GQAttention(Mixer):
             # the step's tokens' values of the first layer that mixes: kept by it, read by the later ones
             v_first = ws.buffer(f"attn.v_first/{self.nkv}x{self.dv}", (T, self.nkv * self.dv), dt)
         if (self.dv == self.d and step.decode_only and cache.k is not None and (cache.writable or self.value_mix is None)
+                and not self.shaped and not self.has_sink
                 and ops.attention_decode_fused_supported(
                     dt, cache.k.dtype, self.nq, self.nkv, self.d, cache.page_size, self.rotary_dim, rope is not None,
                     interleaved=bool(self.mode & ops.ROPE_INTERLEAVED))):
@@ -173,8 +206,13 @@ class GQAttention(Mixer):
             v_lambda=self.v_lambda if self.value_mix == "mixed" else None, v_keep=self.value_mix == "first")
         o = ws.buffer("attn.o", (T, self.nq * self.dv), dt)
         ops.scope("attention.attention")
-        ops.attention(q, o, cache.k, cache.v, step, table, self.window or 0, self.scale,
-                      self.nq, self.nkv, self.d, workspace=ws, decode_chunk=self.decode_chunk, dv=self.dv)
+        if self.shaped:
+            ops.attention_mixed_heads(q, o, cache.k, cache.v, step, table, self.window or 0, self.scale, self.nq, self.nkv,
+                                      self.d, self.dv, sink=self.sink, head_mix=self.mix, dist_r1=self.r1, dist_r2=self.r2,
+                                      softcap=self.softcap, temp_coef=self.temp_coef, temp_every=self.temp_every)
+        else:
+            ops.attention(q, o, cache.k, cache.v, step, table, self.window or 0, self.scale,
+                          self.nq, self.nkv, self.d, workspace=ws, decode_chunk=self.decode_chunk, dv=self.dv, sink=self.sink)
         ops.scope("attention.o_projection")
         linear(o, self.w_o, residual, self.b_o, accumulate=True)
 

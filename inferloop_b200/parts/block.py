@@ -1,5 +1,12 @@
-"""Pre-norm residual block: h += mixer(norm1(h)); h += ffn(norm2(h))
-(crates/model/recipes/src/decoder.rs:112-120 and :474-480)."""
+"""Residual blocks.
+
+Pre-norm (`pre_norm`): h += mixer(norm1(h)); h += ffn(norm2(h))
+(crates/model/recipes/src/decoder.rs:112-120 and :474-480).
+
+Norm on the sublayer's output (`output_norm`): h += norm1(mixer(h)); h += norm2(ffn(h)); and, when the
+layer has one, a third sublayer fed by the token itself: h += norm3(extra(h, token)).  The sublayers read
+the stream as it is (in the compute dtype); each adds into a zeroed 32-bit buffer, and one kernel norms
+that buffer, adds it to the stream, hands the next sublayer its input and zeroes the buffer again."""
 from __future__ import annotations
 
 from typing import List, Mapping
@@ -10,6 +17,7 @@ from ..csrc import ops
 from ..weights.decl import WeightDecl
 from . import registry
 from .base import Block, CacheNeeds
+from .norm import RMSNorm
 
 
 class PreNormBlock(Block):
@@ -64,4 +72,84 @@ class PreNormBlock(Block):
         self.ffn.forward(normed, hidden, step)
 
 
+class OutputNormBlock(Block):
+    """spec: hidden_size; tensor-name pieces mixer_prefix, ffn_prefix, mixer_norm, ffn_norm (under the layer prefix);
+    optionally `extra` (a PartSpec of role feed_forward: the third sublayer), `extra_prefix`, `extra_norm` (the
+    PartSpec of its norm; default: the layer's) and `extra_norm_name`."""
+
+    def __init__(self, spec, ctx, prefix: str = "", layer=None) -> None:
+        super().__init__(spec, ctx, prefix)
+        self.hidden = int(spec["hidden_size"])
+        self.norm1 = registry.build_norm(layer.norm, ctx, prefix + spec.get("mixer_norm", "norm1"), width=self.hidden)
+        self.norm2 = registry.build_norm(layer.norm, ctx, prefix + spec.get("ffn_norm", "norm2"), width=self.hidden)
+        self.mixer = registry.build("mixer", layer.mixer, ctx, prefix + spec.get("mixer_prefix", "mix."))
+        self.ffn = registry.build("feed_forward", layer.feed_forward, ctx, prefix + spec.get("ffn_prefix", "mlp."))
+        self.has_ffn = not getattr(self.ffn, "absent", False)
+        self.extra = self.norm3 = None
+        if spec.get("extra") is not None:
+            self.extra = registry.build("feed_forward", spec["extra"], ctx, prefix + spec.get("extra_prefix", "side."))
+            self.norm3 = registry.build_norm(spec.get("extra_norm") or layer.norm, ctx,
+                                             prefix + spec.get("extra_norm_name", "side.norm"), width=self.hidden)
+        for n in (self.norm1, self.norm2, self.norm3):
+            if n is not None and not isinstance(n, RMSNorm):
+                raise ValueError("output_norm: the norms of a sublayer's output must be RMS norms (plain or in groups)")
+
+    def _sublayers(self):
+        """(norm, run(x, y, step, cache)) in order."""
+        out = [(self.norm1, lambda x, y, step, cache: self.mixer.forward(x, y, step, cache))]
+        if self.has_ffn:
+            out.append((self.norm2, lambda x, y, step, cache: self.ffn.forward(x, y, step)))
+        if self.extra is not None:
+            out.append((self.norm3, lambda x, y, step, cache: self.extra.forward(x, y, step)))
+        return out
+
+    @property
+    def graph_safe(self) -> bool:
+        parts = [self.norm1, self.mixer] + ([self.norm2, self.ffn] if self.has_ffn else []) \
+            + ([self.norm3, self.extra] if self.extra is not None else [])
+        return all(p.graph_safe for p in parts)
+
+    def declare_weights(self) -> List[WeightDecl]:
+        out = self.norm1.declare_weights() + self.mixer.declare_weights()
+        second = self.norm2.declare_weights()
+        if not self.has_ffn:          # the absent sublayer's norm may be stored; it is not read
+            second = [WeightDecl(d.name, d.shape, d.role, d.init, d.root, True) for d in second]
+        out += second + self.ffn.declare_weights()
+        if self.extra is not None:
+            out += self.extra.declare_weights() + self.norm3.declare_weights()
+        return out
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        parts = [self.norm1, self.mixer] + ([self.norm2, self.ffn] if self.has_ffn else []) \
+            + ([self.extra, self.norm3] if self.extra is not None else [])
+        for part in parts:
+            part.bind(tensors)
+
+    def cache_needs(self) -> CacheNeeds:
+        return self.mixer.cache_needs()
+
+    def scratch_bytes(self, tokens: int) -> int:
+        size = torch.empty((), dtype=self.ctx.dtype).element_size()
+        subs = [self.mixer.scratch_bytes(tokens), self.ffn.scratch_bytes(tokens) if self.has_ffn else 0,
+                self.extra.scratch_bytes(tokens) if self.extra is not None else 0]
+        return tokens * self.hidden * (size + 4) + max(subs)
+
+    def forward(self, hidden: torch.Tensor, step, cache) -> None:
+        ws = self.ctx.workspace
+        x = ws.buffer("block.normed", hidden.shape, self.ctx.dtype)          # what a sublayer reads
+        y = ws.buffer("block.sublayer_out", hidden.shape, torch.float32)     # what it adds into
+        subs = self._sublayers()
+        ops.scope("norm")
+        ops.cast_zero(hidden, x, y)
+        for i, (norm, run) in enumerate(subs):
+            ops.scope("mixer" if i == 0 else "feed_forward")
+            run(x, y, step, cache)
+            ops.scope("norm")
+            if i + 1 < len(subs):
+                ops.group_norm_add(y, norm.weight, norm.eps, norm.groups, x=hidden, out=x, zero=True)
+            else:
+                ops.group_norm_add(y, norm.weight, norm.eps, norm.groups, x=hidden)
+
+
 registry.register("block", "pre_norm", PreNormBlock)
+registry.register("block", "output_norm", OutputNormBlock)

@@ -35,6 +35,10 @@ class SwiGLU(FeedForward):
                 raise ValueError(f"swiglu has no tensor role {role!r}")
             names[role] = name
         self.names = {k: prefix + v for k, v in names.items()}
+        # what the gate passes through: "silu" (SwiGLU) or "relu"
+        self.activation = str(spec.get("activation", "silu"))
+        if self.activation not in ops.GATE_ACTIVATIONS:
+            raise ValueError(f"gated feed-forward: unknown activation {self.activation!r}")
         self.w_gate_up = self.w_down = None
         self.fused = False
 
@@ -47,7 +51,8 @@ class SwiGLU(FeedForward):
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         n = self.names
         gate, up = tensors[n["gate"]], tensors[n["up"]]
-        self.fused = (gate.dtype == torch.bfloat16 and self.inter % 64 == 0 and self.hidden % 8 == 0)
+        self.fused = (gate.dtype == torch.bfloat16 and self.inter % 64 == 0 and self.hidden % 8 == 0
+                      and self.activation == "silu")
         if self.fused:
             blocks = self.inter // 64
             self.w_gate_up = torch.stack(
@@ -59,7 +64,7 @@ class SwiGLU(FeedForward):
 
     def scratch_bytes(self, tokens: int) -> int:
         size = torch.empty((), dtype=self.ctx.dtype).element_size()
-        fused = self.ctx.dtype == torch.bfloat16 and self.inter % 64 == 0 and self.hidden % 8 == 0
+        fused = self.ctx.dtype == torch.bfloat16 and self.inter % 64 == 0 and self.hidden % 8 == 0 and self.activation == "silu"
         return tokens * self.inter * size * (1 if fused else 3)
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor, step, accumulate: bool = True) -> None:
@@ -76,7 +81,7 @@ class SwiGLU(FeedForward):
             gate_up = ws.buffer("mlp.gate_up", (T, 2 * self.inter), dt)
             linear(x, self.w_gate_up, gate_up)
             ops.scope("feed_forward.swiglu")
-            ops.silu_mul(gate_up, act)
+            ops.silu_mul(gate_up, act, self.activation)
         ops.scope("feed_forward.down")
         linear(act, self.w_down, residual, accumulate=accumulate)
 

@@ -14,7 +14,7 @@ class WeightDecl:
            keeps a 32-bit tensor as stored and widens a 16-bit one without loss;
            "int" is an integer table held as int32.
     init:  distribution used by the random-weights mode: "normal" N(0, 0.02),
-           "norm" 1 + N(0, 0.1), "bias" N(0, 0.02), "mix" 0.5 + N(0, 0.1), "eye" identity + N(0, 0.1), "around_zero" N(0, 0.1), "decay" N(0, 0.7), "zeros".
+           "norm" 1 + N(0, 0.1), "bias" N(0, 0.02), "mix" 0.5 + N(0, 0.1), "eye" identity + N(0, 0.1), "around_zero" N(0, 0.1), "decay" N(0, 0.7), "positive" 0.02 + |N(0, 0.1)|, "zeros".
     root:  True when the name is not under the model's weight prefix
            (`lm_head.weight`, crates/foundation/spi/src/model.rs:220-226).
     optional: a tensor that a file may hold although the model does not read it (or may leave

@@ -91,7 +91,7 @@ def random_tensor(decl: WeightDecl, seed: int, dtype: torch.dtype,
         raise ValueError("integer tables have no random initialiser")
     if decl.init == "zeros":
         return torch.zeros(decl.shape, dtype=dtype, device=device)
-    if decl.init not in ("normal", "bias", "norm", "mix", "eye", "around_zero", "decay"):
+    if decl.init not in ("normal", "bias", "norm", "mix", "eye", "around_zero", "decay", "positive"):
         raise ValueError(f"unknown initialiser {decl.init!r}")
     count = 1
     for n in decl.shape:
@@ -103,6 +103,8 @@ def random_tensor(decl: WeightDecl, seed: int, dtype: torch.dtype,
         t.mul_(0.1)
     elif decl.init == "decay":               # logarithm of a decay rate: rates from about 1/4 to 4
         t.mul_(0.7)
+    elif decl.init == "positive":            # a rate or a slope that has to stay above zero
+        t.abs_().mul_(0.1).add_(0.02)
     elif decl.init == "mix":                 # coefficients of a learned mixture: around 1/2, away from 0 and 1
         t.mul_(0.1).add_(0.5)
     elif decl.init == "eye":                 # a square matrix near the identity
