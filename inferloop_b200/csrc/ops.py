@@ -645,7 +645,8 @@ def attention_mixed_heads(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Ten
                           block_table: torch.Tensor, window: int, scale: float, nq: int, nkv: int, d: int, dv: int,
                           sink: Optional[torch.Tensor] = None, head_mix: Optional[torch.Tensor] = None,
                           dist_r1: Optional[torch.Tensor] = None, dist_r2: Optional[torch.Tensor] = None,
-                          softcap: float = 0.0, temp_coef: float = 0.0, temp_every: int = 1) -> None:
+                          softcap: float = 0.0, temp_coef: float = 0.0, temp_every: int = 1, workspace=None,
+                          decode_chunk: int = 256) -> None:
     """Causal attention whose scores are capped, shifted by a distance term and mixed across heads before the
     softmax (see attention_mix.cu): s = scale * (1 + temp_coef ln(floor((i + 1) / temp_every) + 1)) q.k;
     s <- softcap tanh(s / softcap); s <- s - r1 ln(1 + r2 (i - j)); z_h = sum_g head_mix[h, g] s_g; softmax with `sink`."""
@@ -657,10 +658,36 @@ def attention_mixed_heads(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Ten
     num_pages, nkv_c, page_size, d_c = k_cache.shape
     if (nkv_c, d_c) != (nkv, d) or tuple(v_cache.shape) != (num_pages, nkv, page_size, dv):
         raise KernelError("attention: cache shape does not match the heads")
+    if (MIX_TC_ENABLED and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and workspace is not None
+            and attention_mix_tc_supported(nq, nkv, d, dv) and q.shape[1] % 8 == 0):
+        # the tensor-core kernel: a block owns 16 tokens of a sequence with all heads; a step of single tokens cuts
+        # every sequence's keys into chunks (by key index alone) whose records a second launch adds in order
+        split = decode_chunk if step.decode_only else 0
+        max_chunks, scratch = 0, None
+        if split:
+            max_chunks = max(1, -(-(block_table.shape[1] * page_size) // split))
+            scratch = workspace.buffer("attn.mix_scratch", (step.n_seqs * max_chunks * nq * (dv + 2),), torch.float32)
+        n_blocks = 0 if split else sum(-(-n // 16) for n in step.h_q_len)
+        _call("attention_mix", "ilb_attention_mix_tc", _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(step.positions),
+              _ptr(step.cu_q), _ptr(block_table), _i(block_table.shape[1]), _i(page_size), _i(num_pages), _i(window or 0), _f(scale),
+              _i(step.n_seqs), _i(n_blocks), _i(nq), _i(nkv), _i(d), _i(dv), _i(q.shape[1]), _i(out.shape[1]), _ptr(sink),
+              _ptr(head_mix), _ptr(dist_r1), _ptr(dist_r2), _f(softcap), _f(temp_coef), _i(temp_every), _i(split), _i(max_chunks),
+              _ptr(scratch), ctypes.c_longlong(0 if scratch is None else scratch.numel()), _stream(q))
+        return
     _call("attention_mix", "ilb_attention_mix", _ptr(q), _ptr(out), _i(_code(q)), _ptr(k_cache), _ptr(v_cache), _i(_code(k_cache)),
           _ptr(step.positions), _ptr(step.seq_of_token), _ptr(block_table), _i(block_table.shape[1]), _i(page_size), _i(num_pages),
           _i(window or 0), _f(scale), _i(q.shape[0]), _i(nq), _i(nkv), _i(d), _i(dv), _i(q.shape[1]), _i(out.shape[1]),
           _ptr(sink), _ptr(head_mix), _ptr(dist_r1), _ptr(dist_r2), _f(softcap), _f(temp_coef), _i(temp_every), _stream(q))
+
+
+MIX_TC_ENABLED = True      # tests switch it off to run the exact kernel on bfloat16
+
+
+def attention_mix_tc_supported(nq: int, nkv: int, d: int, dv: int) -> bool:
+    """Geometries the tensor-core kernel for mixed heads takes: at most 16 heads, head sizes in multiples of 16."""
+    lib = load_module("attention_mix")
+    lib.ilb_attention_mix_tc_supported.restype = ctypes.c_int
+    return bool(lib.ilb_attention_mix_tc_supported(_i(nq), _i(nkv), _i(d), _i(dv)))
 
 
 # --------------------------------------------------------------------------- sampling
