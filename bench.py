@@ -197,8 +197,36 @@ def mamevik_numbers(cfg: dict):
             "state_bytes_per_seq": state}
 
 
+def dalavik_numbers(cfg: dict):
+    """The same for a Dalavik configuration.  A latent layer's cache row is the latent with the shared rotated key part;
+    a layer that reads another layer's rows still reads them (counted), but writes none.  Keys and values of a latent
+    layer are both the row; attention with mixed heads adds the mixing of every pair's scores."""
+    W, V, L = cfg["width"], cfg["vocab"], len(cfg["layers"])
+    side = (cfg.get("token_side") or {}).get("dim", 0)
+    params, kv, attn = 0, 0, 0
+    for layer in cfg["layers"]:
+        m, f = layer["mixer"], layer["mlp"]
+        if layer["type"] == "latent_attention":
+            row, H = m["kv_rank"] + m["rot_dim"], m["heads"]
+            params += (W * m["q_rank"] + m["q_rank"] * H * (m["dim"] + m["rot_dim"]) + (0 if "kv_from" in m else W * row)
+                       + H * (m["dim"] + m["vdim"]) * m["kv_rank"] + H * m["vdim"] * W)
+            kv += row * 2
+            attn += 4 * H * row
+        else:
+            H, G = m["heads"], m["kv_heads"]
+            params += ((H + G) * m["dim"] + G * m["vdim"] + H * m["vdim"]) * W
+            kv += G * (m["dim"] + m["vdim"]) * 2
+            attn += 2 * H * (m["dim"] + m["vdim"]) + 2 * H * H
+        if f is not None:
+            params += 3 * W * f["ff"]
+        params += 2 * W * side
+    return {"layer_params": params / L, "head_params": V * W, "kv_bytes_per_token": kv, "attn_flops_per_pair": attn, "layers": L}
+
+
 def model_numbers(cfg: dict):
     """Parameters the matrix products of one token touch, and bytes of cache per token."""
+    if cfg.get("architecture") == "Dalavik":
+        return dalavik_numbers(cfg)
     if cfg.get("architecture") == "Sufolix":
         return sufolix_numbers(cfg)
     if cfg.get("architecture") == "Mamevik":
@@ -807,6 +835,73 @@ def run_mamevik(args) -> dict:
     return out
 
 
+# ----------------------------------------------------------------------------- the Dalavik decoder beside Sufolix
+def dalavik_config(kind: str, layers: int, width: int, vocab: int, ff: int, side: int) -> dict:
+    """`kind`: "latent" (every layer attends over cached latents with a rotated key part, the queries through a latent of
+    their own; every second layer reads the rows of the layer before it), "heads" (every layer is grouped-query attention
+    whose scores are capped, shifted by distance and mixed across heads, with a sink) or "mixed" (two latent layers, one of
+    the other kind, in turn, the second latent layer reading the first's rows)."""
+    def latent(src):
+        m = {"heads": 16, "dim": 96, "rot_dim": 32, "vdim": 128, "q_rank": 768, "kv_rank": 96, "scale": 128 ** -0.5,
+             "rot": {"base": 10000.0, "dims": 32}}
+        if src is not None:
+            m["kv_from"] = src
+        return {"type": "latent_attention", "mixer": m}
+    heads = {"type": "attention", "mixer": {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
+                                            "q_temp": {"coef": 0.1, "every": 1024}}}
+    out = []
+    for i in range(layers):
+        if kind == "latent":
+            out.append(latent(i - 1 if i % 2 else None))
+        elif kind == "heads":
+            out.append(dict(heads))
+        else:
+            out.append(dict(heads) if i % 3 == 2 else latent(i - 1 if i % 3 == 1 else None))
+    return {"architecture": "Dalavik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5, "groups": 2}, "token_side": {"dim": side},
+            "layers": [dict(l, mlp={"kind": "dense", "ff": ff}) for l in out]}
+
+
+def run_dalavik(args) -> dict:
+    """Decode and prefill of the Dalavik decoder at layer sizes of a real model (latent layers, layers whose heads' scores
+    are mixed, both in turn), each beside the closest model the engine has: the Sufolix decoder with a dense feed-forward at
+    the same width, layers, heads and feed-forward size; with the device time of every op class."""
+    import torch
+    L, W, V, FF, SIDE = args.layers if args.layers != FULL_LAYERS else 8, 2048, 32768, 8192, 64
+    which = ["latent", "heads", "mixed"] if args.dalavik == "all" else [args.dalavik]
+    out = {"metric": "dalavik_vs_sufolix_equal_size", "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic",
+           "steps": args.steps, "warmup": args.warmup, "batch": args.batch, "peaks": peaks(), "cases": {}}
+    arms = {kind: dalavik_config(kind, L, W, V, FF, SIDE) for kind in which}
+    arms["sufolix"] = sufolix_config("dense", L, W, 16, 4, 128, FF, 0, 0, 0, 0, V, 1)
+    arms["sufolix"].pop("streams")
+    for arm, cfg in arms.items():
+        pages = (args.batch * (PROMPT_LEN + args.steps + args.warmup + 64) + PREFILL_LEN) // PAGE + 64
+        bench = Bench(cfg, SEED, pages, max(args.batch, 8), 8192, PREFILL_LEN)
+        with ClockSampler() as clocks:
+            tps, ms, kernels, ctx = bench.decode_device(args.batch, args.steps, args.warmup, arm, PROMPT_LEN)
+        touched = bench.weight_bytes
+        if arm != "sufolix":                  # of the second token table a step reads one row per token, not the table
+            touched -= V * L * SIDE * 2
+        step_bytes = touched + args.batch * ctx * bench.nums["kv_bytes_per_token"]
+        r = {"decode_tokens_per_s": round(tps, 1), "decode_ms_per_step": round(ms, 4), "kernels_per_step": kernels,
+             "decode_frac_of_hbm": round(step_bytes / (ms / 1e3) / 1e9 / bench.pk["hbm_gbs"], 4),
+             "weights_gb": round(bench.weight_bytes / 1e9, 3), "kv_bytes_per_token": bench.nums["kv_bytes_per_token"],
+             "clocks": clocks.summary(), "prefill": bench.prefill_timed(PREFILL_LEN, 3, PREFILL_SAMPLES)}
+        if args.breakdown:
+            r["breakdown"] = bench.breakdown(args.batch, PROMPT_LEN, PREFILL_LEN)
+        out["cases"][arm] = r
+        del bench
+        torch.cuda.empty_cache()
+    out["sizes"] = {"layers": L, "width": W, "vocab": V, "ff": FF, "side": SIDE,
+                    "mixers": {kind: sorted({json.dumps(l["mixer"], sort_keys=True) for l in arms[kind]["layers"]}) for kind in which},
+                    "sufolix": {"heads": 16, "kv_heads": 4, "head_dim": 128}}
+    base = out["cases"]["sufolix"]
+    for kind in which:
+        c = out["cases"][kind]
+        c["decode_ms_per_step_over_sufolix"] = round(c["decode_ms_per_step"] / base["decode_ms_per_step"], 4)
+        c["prefill_ms_over_sufolix"] = round(c["prefill"]["ms"] / base["prefill"]["ms"], 4)
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -825,6 +920,8 @@ def main() -> int:
                     help="the Sufolix decoder beside a Qwen3 model of equal size (decode, prefill, op classes with --breakdown)")
     ap.add_argument("--mamevik", nargs="?", const="all", default=None, choices=["all", "latent", "ssd", "mixed"],
                     help="the Mamevik decoder beside a Sufolix model with routed experts of equal size (decode, prefill, op classes with --breakdown)")
+    ap.add_argument("--dalavik", nargs="?", const="all", default=None, choices=["all", "latent", "heads", "mixed"],
+                    help="the Dalavik decoder beside a Sufolix model with a dense feed-forward of equal size (decode, prefill, op classes with --breakdown)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -848,6 +945,9 @@ def main() -> int:
         return 0
     if args.mamevik:
         print(json.dumps(run_mamevik(args)))
+        return 0
+    if args.dalavik:
+        print(json.dumps(run_dalavik(args)))
         return 0
     result = {"8b": run_8b, "14b-mixed": run_14b_mixed, "32b-long": run_32b_long}[args.config](args)
     print(json.dumps(result))

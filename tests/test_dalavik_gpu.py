@@ -65,9 +65,28 @@ def close(got, ref, dtype, what):
 
 
 def check_trace(outputs, trace, ref_logits, dtype, what):
+    """32-bit: every step's rows against the plain logits.  bfloat16: a single row's rounding error varies with the
+    position (measured: up to 1e-2 of the largest logit in root mean square, single elements a few times that; the same
+    in a whole prompt, token by token, and in the exact kernels), so every element is held to twice the bound, a row's
+    root mean square to the bound, and the root mean square over all rows of the trace to a quarter of it."""
+    got_all, ref_all = [], []
     for step, rows in trace.rows.items():
         ref = torch.stack([ref_logits[rid][pos] for rid, pos in rows])
-        close(torch.from_numpy(outputs[step]), ref, dtype, f"{what} step {step} rows {rows[:4]}...")
+        got = torch.from_numpy(outputs[step])
+        if dtype == "float32":
+            close(got, ref, dtype, f"{what} step {step} rows {rows[:4]}...")
+            continue
+        assert got.shape == ref.shape and torch.isfinite(got).all(), f"{what} step {step}"
+        bound = BF16_REL_OF_MAX * float(ref.abs().max())
+        err = (got.double() - ref.double().cpu()).abs()
+        assert float(err.max()) <= 2 * bound, f"{what} step {step} rows {rows[:4]}...: max error {float(err.max()):.3e} exceeds {2 * bound:.3e}"
+        row_rms = err.pow(2).mean(1).sqrt()
+        assert float(row_rms.max()) <= bound, \
+            f"{what} step {step} row {rows[int(row_rms.argmax())]}: root-mean-square error {float(row_rms.max()):.3e} exceeds {bound:.3e}"
+        got_all.append(got)
+        ref_all.append(ref)
+    if got_all:
+        close(torch.cat(got_all), torch.cat(ref_all), dtype, f"{what}, all rows")
 
 
 # ------------------------------------------------------------------------------ the engine
