@@ -479,7 +479,9 @@ MIX_GEOMETRIES = [  # H, G, d, dv, page, cap, temp, with distance, with mixing, 
     (4, 4, 128, 128, 16, 0.0, None, True, True, False),
     (3, 1, 16, 8, 8, 2.0, (1.0, 1), False, True, True),
     (1, 1, 32, 8, 8, 0.0, None, True, False, True),
-    (6, 3, 96, 80, 32, 20.0, (0.5, 64), True, True, True),
+    (6, 3, 80, 96, 32, 25.0, (0.4, 48), True, True, True),
+    (12, 12, 32, 48, 8, 10.0, (0.2, 100), True, True, True),
+    (16, 16, 64, 128, 16, 0.0, None, False, True, True),
     (16, 4, 128, 128, 16, 15.0, (0.3, 128), True, True, True),
 ]
 
