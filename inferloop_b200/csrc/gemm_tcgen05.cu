@@ -66,6 +66,8 @@ enum Epilogue : int { kStore = 0, kAccumulate = 1, kSwiGLU = 2 };
 // silu(g) * u with the fast reciprocal: the quotient is within 2 ulp, far inside what the
 // bfloat16 result keeps, and an epilogue thread has 128 of these per tile.
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+// The gated unit's epilogue: act(gate) * up with act = silu, or relu when `relu` is set.
+__device__ __forceinline__ float gate_mul(int relu, float g, float u) { return relu ? fmaxf(g, 0.f) * u : silu_mul(g, u); }
 
 // K-major operand tile in shared memory, 128-byte swizzle: rows of 128 bytes, 8-row
 // groups 1024 bytes apart.
@@ -95,6 +97,7 @@ struct Params {
   int cluster;               // > 1: a tile's K ranges belong to the CTAs of one cluster, added through their shared memory
   int tma_out;               // many tokens: the result leaves through shared memory and TMA stores (adds, when accumulating)
   int red_out;               // few tokens, accumulating: the K ranges of a tile are separate CTAs whose shares meet in memory (red.add)
+  int gate_relu;             // the gated epilogue's activation: 0 silu, 1 relu
 };
 
 // Work: first `dp_waves` rounds of WHOLE tiles in wave order (round w: CTA c takes tile
@@ -438,7 +441,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           for (int j = 0; j < 4; ++j) {
             const int m = y0 + cg * 4 + j;
             if (m < p.M && n < n_end) {
-              const float val = sw ? silu_mul(acc[j], up[j]) : acc[j] + bv + old[j];
+              const float val = sw ? gate_mul(p.gate_relu, acc[j], up[j]) : acc[j] + bv + old[j];
               const size_t o = (size_t)m * p.ldo + n;
               if (p.out_f32) ((float*)p.out)[o] = val; else ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(val);
             }
@@ -595,7 +598,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 fetch(cb + 32 * half, g);
                 fetch(cb + 64 + 32 * half, u);
 #pragma unroll
-                for (int c = 0; c < 32; ++c) r[c] = silu_mul(g[c], u[c]);
+                for (int c = 0; c < 32; ++c) r[c] = gate_mul(p.gate_relu, g[c], u[c]);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) piece[4 * half + j] = pack8(r + 8 * j);
               }
@@ -653,7 +656,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                   const int m = y0 + c0 + c;
                   if (m < p.M) {
                     const float g = v[c], u = xch[c * 64 + row];
-                    const float r = silu_mul(g, u);
+                    const float r = gate_mul(p.gate_relu, g, u);
                     const size_t o = (size_t)m * p.ldo + i;
                     if (p.out_f32) ((float*)p.out)[o] = r; else ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(r);
                   }
@@ -671,7 +674,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 const int i0 = (y0 + cb) / 2 + (c0 - cb);
                 float r[32];
 #pragma unroll
-                for (int c = 0; c < CH; ++c) r[c] = silu_mul(g[c], u[c]);
+                for (int c = 0; c < CH; ++c) r[c] = gate_mul(p.gate_relu, g[c], u[c]);
                 if (xr < p.M) {
                   const size_t o = (size_t)xr * p.ldo + i0;
                   const bool full = i0 + CH <= half_n && (p.ldo % 8 == 0) && ((uintptr_t)p.out % 16 == 0) && !p.out_f32;
@@ -847,7 +850,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           const int c = cb + j * cstep, m = y0 + c;
           if (c < BN && m < p.M && n < n_end) {
             const float g = acc[j];
-            const float v = sw ? silu_mul(g, up[j]) : g + bv + old[j];
+            const float v = sw ? gate_mul(p.gate_relu, g, up[j]) : g + bv + old[j];
             const size_t o = (size_t)m * p.ldo + n;
             if (p.out_f32) ((float*)p.out)[o] = v; else ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v);
           }
@@ -895,6 +898,7 @@ struct PairParams {
   int n_whole, rest, split;  // tiles that are one item each; tiles cut into `split` K ranges
   int n_items;               // n_whole + rest * split
   int epilogue, out_f32;
+  int gate_relu;             // the gated epilogue's activation: 0 silu, 1 relu
 };
 
 __global__ void __launch_bounds__(192, 1)
@@ -1071,7 +1075,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             tmem_load_32(taddr + cb + 32 * half, g);
             tmem_load_32(taddr + cb + 64 + 32 * half, u);
 #pragma unroll
-            for (int c = 0; c < 32; ++c) r[c] = silu_mul(g[c], u[c]);
+            for (int c = 0; c < 32; ++c) r[c] = gate_mul(p.gate_relu, g[c], u[c]);
 #pragma unroll
             for (int j = 0; j < 4; ++j) piece[4 * half + j] = pack8(r + 8 * j);
           }
@@ -1560,6 +1564,9 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
   ILB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
               "gemm_tc: K (%d) and the leading dimensions (%d, %d) must be multiples of 8", K, lda, ldw);
   ILB_REQUIRE(((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
+  // 3 from the caller: the gated epilogue with relu as the gate's activation (else silu)
+  const int gate_relu = accumulate == 3 ? 1 : 0;
+  if (gate_relu) accumulate = kSwiGLU;
   ILB_REQUIRE(accumulate >= 0 && accumulate <= 2, "gemm_tc: unknown epilogue %d", accumulate);
   ILB_REQUIRE(accumulate != 1 || out_f32, "gemm_tc: accumulation needs a 32-bit output");
   if (accumulate == 2) {
@@ -1576,6 +1583,7 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
   p.k_blocks = (K + kBlockK - 1) / kBlockK;
   p.epilogue = accumulate;
   p.out_f32 = out_f32;
+  p.gate_relu = gate_relu;
 
   Plan plan{};
   const int es = out_f32 ? 4 : 2, out_cols = accumulate == 2 ? N / 2 : N;
@@ -1590,7 +1598,7 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
       q.bias = bias; q.error_flag = error_flag; q.M = M; q.N = N;
       q.tiles_m = (M + 2 * kTileX - 1) / (2 * kTileX);
       q.k_blocks = p.k_blocks; q.n_whole = pp.n_whole; q.rest = pp.rest; q.split = pp.split; q.n_items = (int)pp.items;
-      q.epilogue = accumulate; q.out_f32 = out_f32;
+      q.epilogue = accumulate; q.out_f32 = out_f32; q.gate_relu = gate_relu;
       CUtensorMap mx, my, mo;
       if (make_map(&mx, A, M, K, lda, kTileX)) return -1;
       if (make_map(&my, W, N, K, ldw, kPairN / 2)) return -1;

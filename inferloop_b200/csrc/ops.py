@@ -780,10 +780,12 @@ def gemm_tc_eligible(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> boo
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
-            accumulate: bool = False, max_ctas: int = 0, swiglu: bool = False) -> None:
+            accumulate: bool = False, max_ctas: int = 0, swiglu: bool = False, gate: str = "silu") -> None:
     """out (+)= a @ w.T (+ bias) on tcgen05 tensor cores (see gemm_tcgen05.cu).  With
     `swiglu`, `w` holds blocks of 64 gate rows followed by their 64 up rows and `out` is
-    [M, N/2] = silu(gate) * up."""
+    [M, N/2] = act(gate) * up, act = `gate` ("silu" or "relu")."""
+    if gate not in ("silu", "relu"):
+        raise KernelError(f"gemm: the gated epilogue has no activation {gate!r}")
     _need(a, "gemm a", torch.bfloat16); _need(w, "gemm w", torch.bfloat16); _need(out, "gemm out")
     _need(bias, "gemm bias", torch.float32)
     M, K = a.shape
@@ -794,7 +796,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[
     if accumulate and (out.dtype != torch.float32 or swiglu):
         raise KernelError("gemm: accumulation needs a 32-bit output and no SwiGLU epilogue")
     st = _tc_state(a.device)
-    mode = 2 if swiglu else (1 if accumulate else 0)
+    mode = (3 if gate == "relu" else 2) if swiglu else (1 if accumulate else 0)
     _call("gemm_tcgen05", "ilb_gemm_tc", _ptr(a), _ptr(w), _ptr(bias), _ptr(out),
           _i(1 if out.dtype == torch.float32 else 0), _i(M), _i(N), _i(K), _i(a.stride(0)), _i(w.stride(0)),
           _i(out.stride(0)), _i(mode), _ptr(st.workspace), ctypes.c_longlong(st.floats),

@@ -69,6 +69,7 @@ class StepContext:
     max_kv_len: int = 0
     decode_only: bool = False
     position_tables: Dict[object, torch.Tensor] = field(default_factory=dict)
+    memo: Dict[str, object] = field(default_factory=dict)    # what one part of a step leaves for the next one to run
 
 
 class StepStager:

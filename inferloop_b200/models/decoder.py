@@ -118,6 +118,8 @@ class DecoderModel:
     def forward_embed(self, step, caches=None) -> torch.Tensor:
         s = self.spec
         hidden = self.hidden_buffer(step.n_tokens)
+        if getattr(step, "memo", None):            # (a step object may be used again: nothing is left over from its last pass)
+            step.memo.clear()
         ops.scope("embedding")
         if self.embed_part is not None:
             self.embed_part.forward(step, self.embedding, hidden, caches.model_state() if caches is not None else {})
@@ -128,8 +130,15 @@ class DecoderModel:
 
     def forward_entries(self, hidden: torch.Tensor, step, caches, first: int, last: int) -> None:
         """Run-order entries first .. last - 1."""
+        memo = getattr(step, "memo", None)
+        if memo and first == 0:
+            memo.clear()
         for entry in self.spec.run_order[first:last]:
-            self.blocks[entry.layer].forward(hidden, step, caches.layer_cache(entry))
+            block = self.blocks[entry.layer]
+            if memo:                       # what a block left for its successor holds only for a block of its own kind
+                for key in [k for k in memo if k != getattr(block, "PREPARED", None)]:
+                    del memo[key]
+            block.forward(hidden, step, caches.layer_cache(entry))
 
     def forward_head(self, hidden: torch.Tensor, step) -> torch.Tensor:
         s, ws = self.spec, self.ctx.workspace

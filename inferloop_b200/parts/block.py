@@ -94,6 +94,8 @@ class OutputNormBlock(Block):
             if n is not None and not isinstance(n, RMSNorm):
                 raise ValueError("output_norm: the norms of a sublayer's output must be RMS norms (plain or in groups)")
 
+    PREPARED = "output_norm.prepared"       # memo key: (stream, copy, buffer, shape) that the block before left ready
+
     def _sublayers(self):
         """(norm, run(x, y, step, cache)) in order."""
         out = [(self.norm1, lambda x, y, step, cache: self.mixer.forward(x, y, step, cache))]
@@ -139,16 +141,23 @@ class OutputNormBlock(Block):
         x = ws.buffer("block.normed", hidden.shape, self.ctx.dtype)          # what a sublayer reads
         y = ws.buffer("block.sublayer_out", hidden.shape, torch.float32)     # what it adds into
         subs = self._sublayers()
-        ops.scope("norm")
-        ops.cast_zero(hidden, x, y)
+        # The last norm of a block also leaves the stream's copy and the zeroed buffer for the block that runs
+        # next; the step's memo says so (the decoder forgets it before a block of another kind).
+        memo = getattr(step, "memo", None)
+        prepared = (hidden.data_ptr(), x.data_ptr(), y.data_ptr(), tuple(hidden.shape))
+        if memo is None or memo.pop(self.PREPARED, None) != prepared:
+            ops.scope("norm")
+            ops.cast_zero(hidden, x, y)
         for i, (norm, run) in enumerate(subs):
             ops.scope("mixer" if i == 0 else "feed_forward")
             run(x, y, step, cache)
             ops.scope("norm")
-            if i + 1 < len(subs):
+            if i + 1 < len(subs) or memo is not None:
                 ops.group_norm_add(y, norm.weight, norm.eps, norm.groups, x=hidden, out=x, zero=True)
             else:
                 ops.group_norm_add(y, norm.weight, norm.eps, norm.groups, x=hidden)
+        if memo is not None:
+            memo[self.PREPARED] = prepared
 
 
 registry.register("block", "pre_norm", PreNormBlock)

@@ -51,8 +51,7 @@ class SwiGLU(FeedForward):
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         n = self.names
         gate, up = tensors[n["gate"]], tensors[n["up"]]
-        self.fused = (gate.dtype == torch.bfloat16 and self.inter % 64 == 0 and self.hidden % 8 == 0
-                      and self.activation == "silu")
+        self.fused = gate.dtype == torch.bfloat16 and self.inter % 64 == 0 and self.hidden % 8 == 0
         if self.fused:
             blocks = self.inter // 64
             self.w_gate_up = torch.stack(
@@ -64,7 +63,7 @@ class SwiGLU(FeedForward):
 
     def scratch_bytes(self, tokens: int) -> int:
         size = torch.empty((), dtype=self.ctx.dtype).element_size()
-        fused = self.ctx.dtype == torch.bfloat16 and self.inter % 64 == 0 and self.hidden % 8 == 0 and self.activation == "silu"
+        fused = self.ctx.dtype == torch.bfloat16 and self.inter % 64 == 0 and self.hidden % 8 == 0
         return tokens * self.inter * size * (1 if fused else 3)
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor, step, accumulate: bool = True) -> None:
@@ -72,9 +71,9 @@ class SwiGLU(FeedForward):
         T = x.shape[0]
         ws, dt = self.ctx.workspace, self.ctx.dtype
         act = ws.buffer("mlp.act", (T, self.inter), dt)
-        ops.scope("feed_forward.gate_up (SwiGLU inside)" if self.fused else "feed_forward.gate_up")
+        ops.scope("feed_forward.gate_up (gate inside)" if self.fused else "feed_forward.gate_up")
         if self.fused and ops.gemm_tc_eligible(x, self.w_gate_up, act):
-            ops.gemm_tc(x, self.w_gate_up, act, swiglu=True)
+            ops.gemm_tc(x, self.w_gate_up, act, swiglu=True, gate=self.activation)
         elif self.fused:
             raise ops.KernelError("SwiGLU: the interleaved weight needs the tensor-core GEMM, which refused this input")
         else:

@@ -360,6 +360,26 @@ def test_relu_gate_of_the_feed_forward(dtype):
         assert_close(out, ref, name_of(dtype), "relu gate", bf16_rel_of_max=2.0 ** -8)
 
 
+@pytest.mark.parametrize("tokens", [1, 8, 70, 300])
+@pytest.mark.parametrize("gate", ["relu", "silu"])
+def test_the_gate_inside_the_tensor_core_product(tokens, gate):
+    """relu(gate) * up (or silu) formed in the epilogue of the product over the weight whose rows interleave
+    blocks of 64 gate rows and 64 up rows, for a single token, a few, and many tokens."""
+    from inferloop_b200.csrc import ops
+    g = torch.Generator().manual_seed(7 + tokens)
+    width, inter = 192, 320 if tokens < 100 else 1024
+    x = torch.randn(tokens, width, generator=g).bfloat16()
+    wg = (torch.randn(inter, width, generator=g) / width ** 0.5).bfloat16()
+    wu = (torch.randn(inter, width, generator=g) / width ** 0.5).bfloat16()
+    blocks = inter // 64
+    w = torch.stack([wg.view(blocks, 64, width), wu.view(blocks, 64, width)], dim=1).reshape(2 * inter, width).contiguous()
+    out = torch.empty(tokens, inter, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc(x.to(DEV), w.to(DEV), out, swiglu=True, gate=gate)
+    a, b = x.double() @ wg.double().T, x.double() @ wu.double().T
+    ref = (torch.relu(a) if gate == "relu" else a * torch.sigmoid(a)) * b
+    assert_close(out, ref, "bfloat16", f"{gate} gate in the product, {tokens} tokens", bf16_rel_of_max=2.0 ** -7)
+
+
 def paged(rows, page, order):
     """rows [n, width] laid into pages in the order given: (cache [pages, 1, page, width], block table row)."""
     n, width = rows.shape
