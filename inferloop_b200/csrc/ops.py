@@ -665,6 +665,10 @@ def attention_mixed_heads(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Ten
         split = decode_chunk if step.decode_only else 0
         max_chunks, scratch = 0, None
         if split:
+            # the chunk depends on the width of the block table alone (a constant of the engine, not of the batch):
+            # at most MIX_MAX_CHUNKS records a sequence
+            while block_table.shape[1] * page_size > split * MIX_MAX_CHUNKS:
+                split *= 2
             max_chunks = max(1, -(-(block_table.shape[1] * page_size) // split))
             scratch = workspace.buffer("attn.mix_scratch", (step.n_seqs * max_chunks * nq * (dv + 2),), torch.float32)
         n_blocks = 0 if split else sum(-(-n // 16) for n in step.h_q_len)
@@ -681,6 +685,7 @@ def attention_mixed_heads(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Ten
 
 
 MIX_TC_ENABLED = True      # tests switch it off to run the exact kernel on bfloat16
+MIX_MAX_CHUNKS = 64        # the most chunk records of a single token's keys (the scratch a sequence needs)
 
 
 def attention_mix_tc_supported(nq: int, nkv: int, d: int, dv: int) -> bool:

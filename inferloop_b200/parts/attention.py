@@ -210,7 +210,7 @@ class GQAttention(Mixer):
             ops.attention_mixed_heads(q, o, cache.k, cache.v, step, table, self.window or 0, self.scale, self.nq, self.nkv,
                                       self.d, self.dv, sink=self.sink, head_mix=self.mix, dist_r1=self.r1, dist_r2=self.r2,
                                       softcap=self.softcap, temp_coef=self.temp_coef, temp_every=self.temp_every,
-                                      workspace=ws, decode_chunk=self.decode_chunk)
+                                      workspace=ws, decode_chunk=ops.DECODE_CHUNK_MIN)
         else:
             ops.attention(q, o, cache.k, cache.v, step, table, self.window or 0, self.scale,
                           self.nq, self.nkv, self.d, workspace=ws, decode_chunk=self.decode_chunk, dv=self.dv, sink=self.sink)
