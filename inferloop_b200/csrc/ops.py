@@ -685,7 +685,7 @@ def attention_mixed_heads(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Ten
 
 
 MIX_TC_ENABLED = True      # tests switch it off to run the exact kernel on bfloat16
-MIX_MAX_CHUNKS = 64        # the most chunk records of a single token's keys (the scratch a sequence needs)
+MIX_MAX_CHUNKS = 512       # the most chunk records of a single token's keys (131,072 keys in chunks of 256; 4 MB of scratch a sequence at 16 heads of 128)
 
 
 def attention_mix_tc_supported(nq: int, nkv: int, d: int, dv: int) -> bool:

@@ -213,6 +213,23 @@ def test_a_long_prompt_whole_and_in_portions(root, name, dtype):
         close(torch.cat(rows), whole, dtype, f"{name} portions of {portion} against the whole prompt")
 
 
+@pytest.mark.parametrize("name,dtype", [("Q", "bfloat16"), ("Q", "float32")])
+def test_single_tokens_on_both_sides_of_a_chunk_of_keys(root, name, dtype):
+    """Two unequal requests decode together while one of them passes key 256, where the kernel for single tokens
+    starts a second chunk of keys (its first token there reads one key of the new chunk); the other stays
+    inside its first chunk.  Each against the plain model of its own tokens."""
+    toks = {"a": tokens_for(name, 270, 11), "b": tokens_for(name, 60, 12)}
+    ref = {k: reference(root, name, dtype, v) for k, v in toks.items()}
+    page = cases.CASES[name][2]
+    r = runner_for(root, name, dtype, pages=-(-270 // page) + -(-60 // page) + 2)
+    t = Trace()
+    t.step([("a", toks["a"][:250], [0, 249]), ("b", toks["b"][:40], [39])])
+    for i in range(20):
+        t.step([("a", [toks["a"][250 + i]], [0]), ("b", [toks["b"][40 + i]], [0])], end=["a", "b"] if i == 19 else [])
+    check_trace(run_trace_inprocess(r, t), t, ref, dtype, f"{name} two requests around key 256")
+    r.cache.check()
+
+
 @pytest.mark.parametrize("name,dtype", [("P", "float32"), ("Q", "bfloat16"), ("R", "float32")])
 def test_greedy_generation_through_the_entry_point(root, name, dtype):
     from inferloop_b200 import Engine, SamplingParams
