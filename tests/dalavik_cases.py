@@ -67,7 +67,15 @@ CONFIG_R = model(130, 64, 1e-5, 1, None, [
     layer(attn(1, 1, 32, 8, 0.2, softcap=2.0), None),
     layer(latent(6, 8, 2, 8, 32, 24, 0.3, kv_from=1), 16),
 ])
-CASES = {"P": (CONFIG_P, 31, 4), "Q": (CONFIG_Q, 32, 16), "R": (CONFIG_R, 33, 8)}       # config, seed, page size
+# S: nothing is a multiple of eight: a width of 70 in five norm groups, odd ranks, head sizes, feed-forward and side
+# sizes, rows of 11 and 21 cached elements, seven query heads on one kv head.
+CONFIG_S = model(97, 70, 2e-5, 5, 3, [
+    layer(latent(2, 6, 2, 5, 7, 9, 0.4, base=100.0), 45),
+    layer(attn(7, 1, 9, 11, 0.3, softcap=4.0, q_temp=(0.3, 5)), 30),
+    layer(latent(3, 5, 2, 7, 11, 9, 0.4, base=100.0, kv_from=0), None),
+    layer(latent(1, 10, 6, 3, 5, 15, 0.3), 19),
+])
+CASES = {"P": (CONFIG_P, 31, 4), "Q": (CONFIG_Q, 32, 16), "R": (CONFIG_R, 33, 8), "S": (CONFIG_S, 34, 4)}   # config, seed, page size
 
 _FOLDERS: Dict[tuple, str] = {}
 _PLAIN: Dict[tuple, "Plain"] = {}

@@ -19,7 +19,7 @@ from helpers import ROOT, Trace, assert_close, random_tokens, run_trace_inproces
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
-ENGINE_CASES = [(n, d) for n in ("P", "Q", "R") for d in ("float32", "bfloat16")]
+ENGINE_CASES = [(n, d) for n in ("P", "Q", "R", "S") for d in ("float32", "bfloat16")]
 
 
 @pytest.fixture(scope="module")
