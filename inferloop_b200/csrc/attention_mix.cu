@@ -230,7 +230,9 @@ struct MixTcParams {
   float softcap, temp_coef;
   int temp_every;
   int split_chunk, max_chunks;
-  float* scratch;                              // [n_seqs][max_chunks][nq][dv + 2]
+  float* scratch;                              // [n_seqs or n_tokens][max_chunks][nq][dv + 2]
+  int per_token;                               // the chunks' records belong to tokens of prompt portions (else to single tokens, by sequence)
+  int n_tokens;
 };
 
 __device__ __forceinline__ void mix_cp_async_16(uint32_t dst, const void* src, int src_bytes) {
@@ -286,8 +288,13 @@ attention_mix_tc_kernel(const MixTcParams a) {
   const int n_rows = min(kTcRows, a.cu_q[seq + 1] - t0);
   const int p0 = a.positions[t0];                 // the rows' positions are p0, p0 + 1, ...
   const int p_last = p0 + n_rows - 1;
-  int key_lo = (a.window > 0 && p0 + 1 > a.window) ? p0 + 1 - a.window : 0;
-  const int key_hi = p_last + 1;
+  int key_lo = (a.window > 0 && p0 + 1 > a.window) ? p0 + 1 - a.window : 0, key_hi = p_last + 1;
+  const int chunk = a.per_token ? blockIdx.y : 0;
+  if (a.per_token) {                              // few blocks with many keys: block (16 tokens, chunk of keys) leaves records
+    key_lo = max(key_lo, chunk * a.split_chunk);
+    key_hi = min(key_hi, (chunk + 1) * a.split_chunk);
+    if (key_lo >= key_hi) return;
+  }
   key_lo = key_lo / kTcKeys * kTcKeys;            // tiles start at multiples of 32 keys: the walk depends on positions alone
   const int* table = a.block_table + (size_t)seq * a.max_blocks;
 
@@ -483,6 +490,23 @@ attention_mix_tc_kernel(const MixTcParams a) {
   if (!head_warp) return;
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  if (a.per_token) {
+    // the chunk's record of each of the block's tokens: max, sum, weighted values
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = gq + 8 * half;
+      if (r >= n_rows) continue;
+      float* rec = a.scratch + (((size_t)(t0 + r) * a.max_chunks + chunk) * H + h) * (dv + 2);
+      if (tq == 0) { rec[0] = half ? m1 : m0; rec[1] = half ? l1 : l0; }
+#pragma unroll
+      for (int i = 0; i < DV / 8; ++i) {
+        if (i * 8 >= dv) break;
+        rec[2 + i * 8 + 2 * tq] = o[i][2 * half];
+        rec[2 + i * 8 + 2 * tq + 1] = o[i][2 * half + 1];
+      }
+    }
+    return;
+  }
   float g0 = 1.0f, g1 = 1.0f;
   if (a.sink != nullptr) {
     const float sk = a.sink[h], top0 = fmaxf(m0, sk), top1 = fmaxf(m1, sk);
@@ -499,13 +523,15 @@ attention_mix_tc_kernel(const MixTcParams a) {
   }
 }
 
-// The chunks' records of a single token added in chunk order, with the sink: a thread an output element.
+// The chunks' records of a token added in chunk order, with the sink: a thread an output element.
 __global__ void __launch_bounds__(256)
 attention_mix_merge_kernel(const MixTcParams a) {
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();
-  const int seq = blockIdx.x, H = a.nq, dv = a.dv;
-  const int t = a.cu_q[seq], p = a.positions[t];
+  const int H = a.nq, dv = a.dv;
+  const int t = a.per_token ? blockIdx.x : a.cu_q[blockIdx.x];       // the token, and whose records these are
+  const int seq = a.per_token ? t : blockIdx.x;
+  const int p = a.positions[t];
   const int lo = (a.window > 0 && p + 1 > a.window) ? p + 1 - a.window : 0;
   const int c_lo = lo / a.split_chunk, c_hi = p / a.split_chunk;
   const int e = blockIdx.y * blockDim.x + threadIdx.x;            // a thread an output element
@@ -778,13 +804,15 @@ ILB_EXPORT int ilb_attention_mix_tc_supported(int nq, int nkv, int d, int dv) {
   return mix_tc_smem(nq, nkv, d, dv) <= 220 * 1024 ? 1 : 0;
 }
 
-// n_blocks: the blocks of 16 tokens over all sequences (split_chunk 0), else ignored: the grid is (sequences, max_chunks).
+// n_blocks: the blocks of 16 tokens over all sequences.  split_chunk > 0 without per_token: single tokens, the grid is
+// (sequences, max_chunks).  With per_token: prompt portions whose blocks are few and whose keys are many; the grid is
+// (n_blocks, max_chunks) and a second launch adds every token's records.
 ILB_EXPORT int ilb_attention_mix_tc(
     const void* q, void* out, const void* k_cache, const void* v_cache, const int* positions, const int* cu_q,
     const int* block_table, int max_blocks, int page_size, int num_pages, int window, float scale, int n_seqs, int n_blocks,
     int nq, int nkv, int d, int dv, int q_stride, int out_stride, const float* sink, const float* talk, const float* r1,
     const float* r2, float softcap, float temp_coef, int temp_every, int split_chunk, int max_chunks, float* scratch,
-    long long scratch_floats, cudaStream_t stream) {
+    long long scratch_floats, int per_token, int n_tokens, cudaStream_t stream) {
   ILB_REQUIRE(ilb_attention_mix_tc_supported(nq, nkv, d, dv), "attention_mix_tc: %d / %d heads of %d / %d are not served", nq, nkv, d, dv);
   ILB_REQUIRE(page_size > 0 && max_blocks > 0 && num_pages > 0 && window >= 0 && softcap >= 0.f, "attention_mix_tc: bad arguments");
   ILB_REQUIRE((r1 == nullptr) == (r2 == nullptr), "attention_mix_tc: the distance term needs both of its vectors");
@@ -792,15 +820,20 @@ ILB_EXPORT int ilb_attention_mix_tc(
   ILB_REQUIRE(q_stride >= nq * d && out_stride >= nq * dv && q_stride % 8 == 0 && out_stride % 2 == 0 && ((uintptr_t)q % 16 == 0) &&
               ((uintptr_t)out % 4 == 0) && ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0),
               "attention_mix_tc: rows are not aligned");
-  ILB_REQUIRE(split_chunk >= 0 && (split_chunk == 0 || (split_chunk % kTcKeys == 0 && max_chunks > 0 && scratch != nullptr &&
-              (long long)max_blocks * page_size <= (long long)max_chunks * split_chunk &&
-              scratch_floats >= (long long)n_seqs * max_chunks * nq * (dv + 2))),
+  ILB_REQUIRE(split_chunk >= 0 && (split_chunk == 0 || (split_chunk % kTcKeys == 0 && max_chunks > 0 && scratch != nullptr)),
+              "attention_mix_tc: chunks are multiples of %d keys and need a scratch", kTcKeys);
+  ILB_REQUIRE(split_chunk == 0 || per_token != 0 || ((long long)max_blocks * page_size <= (long long)max_chunks * split_chunk &&
+              scratch_floats >= (long long)n_seqs * max_chunks * nq * (dv + 2)),
               "attention_mix_tc: the chunks do not cover the block table, or the scratch is too small");
+  ILB_REQUIRE(per_token == 0 || (split_chunk > 0 && n_tokens > 0 && n_blocks > 0 &&
+              scratch_floats >= (long long)n_tokens * max_chunks * nq * (dv + 2)),
+              "attention_mix_tc: records by token need chunks, the blocks and a scratch for every token");
   if (n_seqs == 0 || (split_chunk == 0 && n_blocks == 0)) return 0;
   const MixTcParams a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
                       positions, cu_q, block_table, max_blocks, page_size, num_pages, window, scale, n_seqs, nq, nkv, d, dv,
-                      q_stride, out_stride, sink, talk, r1, r2, softcap, temp_coef, temp_every, split_chunk, max_chunks, scratch};
-  if (split_chunk > 0) {
+                      q_stride, out_stride, sink, talk, r1, r2, softcap, temp_coef, temp_every, split_chunk, max_chunks, scratch,
+                      per_token, n_tokens};
+  if (split_chunk > 0 && !per_token) {
     // single tokens: the heads are the rows of the tiles; the chunks' records are added by a second launch
     const int kt = mix_heads_tile(nq, nkv, d, dv, split_chunk);
     ILB_REQUIRE(kt > 0, "attention_mix_tc: no key tile fits chunks of %d keys", split_chunk);
@@ -822,7 +855,7 @@ ILB_EXPORT int ilb_attention_mix_tc(
     return check_launch("attention_mix_merge");
   }
   const size_t smem = mix_tc_smem(nq, nkv, d, dv);
-  const dim3 grid = dim3(n_blocks);
+  const dim3 grid = per_token ? dim3(n_blocks, max_chunks) : dim3(n_blocks);
 #define ILB_TC(DV)                                                                                                        \
   do {                                                                                                                    \
     static OncePerDevice once;                                                                                            \
@@ -835,7 +868,12 @@ ILB_EXPORT int ilb_attention_mix_tc(
   } while (0)
   if (dv <= 64) ILB_TC(64); else ILB_TC(128);
 #undef ILB_TC
-  return check_launch("attention_mix_tc");
+  if (check_launch("attention_mix_tc") != 0) return -1;
+  if (per_token) {
+    ilb::launch(attention_mix_merge_kernel, dim3(n_tokens, (nq * dv + 255) / 256), dim3(256), 0, stream, a);
+    return check_launch("attention_mix_merge");
+  }
+  return 0;
 }
 
 ILB_DEFINE_LAST_ERROR()

@@ -672,11 +672,20 @@ def attention_mixed_heads(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Ten
             max_chunks = max(1, -(-(block_table.shape[1] * page_size) // split))
             scratch = workspace.buffer("attn.mix_scratch", (step.n_seqs * max_chunks * nq * (dv + 2),), torch.float32)
         n_blocks = 0 if split else sum(-(-n // 16) for n in step.h_q_len)
+        per_token = 0
+        if not split and n_blocks <= MIX_FEW_BLOCKS and step.max_kv_len > MIX_PROMPT_CHUNK:
+            # few blocks of 16 tokens with many keys each (a long prompt alone): the blocks also cut their keys into
+            # chunks, so that the longest walk is a chunk and not the whole prompt; a second launch adds a token's records
+            chunks = -(-step.max_kv_len // MIX_PROMPT_CHUNK)
+            floats = q.shape[0] * chunks * nq * (dv + 2)
+            if floats * 4 <= MIX_PROMPT_SCRATCH_BYTES:
+                per_token, split, max_chunks = 1, MIX_PROMPT_CHUNK, chunks
+                scratch = workspace.buffer("attn.mix_scratch", (floats,), torch.float32)
         _call("attention_mix", "ilb_attention_mix_tc", _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(step.positions),
               _ptr(step.cu_q), _ptr(block_table), _i(block_table.shape[1]), _i(page_size), _i(num_pages), _i(window or 0), _f(scale),
               _i(step.n_seqs), _i(n_blocks), _i(nq), _i(nkv), _i(d), _i(dv), _i(q.shape[1]), _i(out.shape[1]), _ptr(sink),
               _ptr(head_mix), _ptr(dist_r1), _ptr(dist_r2), _f(softcap), _f(temp_coef), _i(temp_every), _i(split), _i(max_chunks),
-              _ptr(scratch), ctypes.c_longlong(0 if scratch is None else scratch.numel()), _stream(q))
+              _ptr(scratch), ctypes.c_longlong(0 if scratch is None else scratch.numel()), _i(per_token), _i(q.shape[0]), _stream(q))
         return
     _call("attention_mix", "ilb_attention_mix", _ptr(q), _ptr(out), _i(_code(q)), _ptr(k_cache), _ptr(v_cache), _i(_code(k_cache)),
           _ptr(step.positions), _ptr(step.seq_of_token), _ptr(block_table), _i(block_table.shape[1]), _i(page_size), _i(num_pages),
@@ -685,6 +694,9 @@ def attention_mixed_heads(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Ten
 
 
 MIX_TC_ENABLED = True      # tests switch it off to run the exact kernel on bfloat16
+MIX_PROMPT_CHUNK = 1024    # keys a block of 16 tokens walks when the blocks of a step are few and their keys many
+MIX_FEW_BLOCKS = 296       # "few": up to two blocks a multiprocessor
+MIX_PROMPT_SCRATCH_BYTES = 256 << 20
 MIX_MAX_CHUNKS = 512       # the most chunk records of a single token's keys (131,072 keys in chunks of 256; 4 MB of scratch a sequence at 16 heads of 128)
 
 

@@ -577,6 +577,14 @@ def test_attention_with_shaped_and_mixed_scores(geometry, dtype, kernel):
         ops.attention_mixed_heads(q.view(-1, H * d)[rows].to(DEV).contiguous(), out1, k_cache.to(DEV), v_cache.to(DEV), singles,
                                   table[:3].contiguous(), 0, scale, H, G, d, dv, **args)
         got1 = out1.float().cpu()
+        # the same launch as the first, with the blocks' keys cut into chunks of 64 (as few blocks with many keys are):
+        # portions that end inside a chunk, at positions before and after several borders, beside single tokens
+        chunk, ops.MIX_PROMPT_CHUNK = ops.MIX_PROMPT_CHUNK, 64
+        try:
+            out2 = torch.zeros(sum(lens), H * dv, dtype=dtype, device=DEV)
+            ops.attention_mixed_heads(q.view(-1, H * d).to(DEV), out2, k_cache.to(DEV), v_cache.to(DEV), step, table, 0, scale, H, G, d, dv, **args)
+        finally:
+            ops.MIX_PROMPT_CHUNK = chunk
     dd = lambda t: None if t is None else t.double()
     ref = shaped_attention_reference(q.double(), k.double(), v.double(), step.positions.cpu(), scale, per, cap, temp,
                                      dd(r1), dd(r2), dd(mix), dd(sink))
@@ -584,6 +592,7 @@ def test_attention_with_shaped_and_mixed_scores(geometry, dtype, kernel):
     assert_close(out.float().cpu().view(-1, H, dv), ref, name_of(dtype), "attention with mixed heads", bf16_rel_of_max=bound)
     if kernel == "tensor cores":
         assert_close(got1.view(3, H, dv), ref[rows], "bfloat16", "single tokens in chunks", bf16_rel_of_max=bound)
+        assert_close(out2.float().cpu().view(-1, H, dv), ref, "bfloat16", "portions with their keys in chunks", bf16_rel_of_max=bound)
     # the hot keys carry weight: without them the result differs by far more than the bound
     k2 = k.double().clone()
     k2[3, 0] = 0
