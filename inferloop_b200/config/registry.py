@@ -102,10 +102,12 @@ def default_registry() -> ArchitectureRegistry:
         from ..models.sufolix import ARCHITECTURE as SUFOLIX
         from ..models.mamevik import ARCHITECTURE as MAMEVIK
         from ..models.dalavik import ARCHITECTURE as DALAVIK
+        from ..models.zebivik import ARCHITECTURE as ZEBIVIK
         _DEFAULT.register(ARCHITECTURE)
         _DEFAULT.register(SUFOLIX)
         _DEFAULT.register(MAMEVIK)
         _DEFAULT.register(DALAVIK)
+        _DEFAULT.register(ZEBIVIK)
     return _DEFAULT
 
 

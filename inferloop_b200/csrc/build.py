@@ -45,6 +45,7 @@ MODULES: Dict[str, List[str]] = {
     "latent": [],
     "sublayer_norm": [],
     "attention_mix": [],
+    "recurrent": [],
 }
 
 _LOCK = threading.Lock()

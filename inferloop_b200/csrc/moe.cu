@@ -130,7 +130,8 @@ ILB_EXPORT int ilb_moe_logits(const void* x, const void* w, int dtype, float* ou
 // One warp per token.
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int ld, int n_tokens, int experts, int top,
-                 int softmax, int renormalize, int* __restrict__ choice, float* __restrict__ weight) {
+                 int softmax, int renormalize, int* __restrict__ choice, float* __restrict__ weight,
+                 const float* __restrict__ correction, int groups, int keep, float out_scale, float renorm_eps) {
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -163,6 +164,49 @@ moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bia
     for (int i = 0; i < kMaxExpertsPerLane; ++i)
       if (lane + 32 * i < experts) s[i] = sigmoid_stable(s[i]);
   }
+  // What the experts are ranked by: the scores, or the scores plus a stored correction (the weights below are the
+  // scores themselves either way).  With groups, only experts of the `keep` groups of neighbours whose best ranked
+  // member is largest can be chosen (ties to the lower group).
+  float c[kMaxExpertsPerLane];
+#pragma unroll
+  for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+    const int e = lane + 32 * i;
+    c[i] = (e < experts && correction != nullptr) ? s[i] + correction[e] : s[i];
+  }
+  if (groups > 1 && keep < groups) {
+    const int per = experts / groups;
+    float mine = -INFINITY;                // lane g: group g's best member
+    for (int g = 0; g < groups; ++g) {
+      float m = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+        const int e = lane + 32 * i;
+        if (e < experts && e / per == g) m = fmaxf(m, c[i]);
+      }
+      m = warp_max(m);
+      if (lane == g) mine = m;
+    }
+    unsigned allowed = 0u;
+    for (int j = 0; j < keep; ++j) {
+      float best = mine;
+      int best_g = (lane < groups && mine != -INFINITY) ? lane : 0x7fffffff;
+      if (best_g == 0x7fffffff) best = -INFINITY;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int og = __shfl_xor_sync(0xffffffffu, best_g, o);
+        if (ob > best || (ob == best && og < best_g)) { best = ob; best_g = og; }
+      }
+      if (best_g == 0x7fffffff) break;
+      allowed |= 1u << best_g;
+      if (lane == best_g) mine = -INFINITY;
+    }
+#pragma unroll
+    for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+      const int e = lane + 32 * i;
+      if (e < experts && !((allowed >> (e / per)) & 1u)) c[i] = -INFINITY;
+    }
+  }
   float chosen_w = 0.f, total = 0.f;     // lane j keeps the j-th choice
   int chosen_e = 0;
   for (int j = 0; j < top; ++j) {
@@ -171,7 +215,7 @@ moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bia
 #pragma unroll
     for (int i = 0; i < kMaxExpertsPerLane; ++i) {
       const int e = lane + 32 * i;
-      if (e < experts && (s[i] > best || (s[i] == best && e < best_e)) && s[i] != -INFINITY) { best = s[i]; best_e = e; }
+      if (e < experts && (c[i] > best || (c[i] == best && e < best_e)) && c[i] != -INFINITY) { best = c[i]; best_e = e; }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -180,15 +224,18 @@ moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bia
       if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
     }
     if (best_e == 0x7fffffff) { best_e = 0; best = 0.f; }      // (non-finite logits: keep the indices in range)
+    float score = 0.f;                                          // the winner's score, from the lane that holds it
 #pragma unroll
     for (int i = 0; i < kMaxExpertsPerLane; ++i)
-      if (lane + 32 * i == best_e) s[i] = -INFINITY;            // taken
-    if (lane == j) { chosen_w = best; chosen_e = best_e; }
-    total += best;
+      if (lane + 32 * i == best_e) { score = s[i]; c[i] = -INFINITY; }      // taken
+    score = __shfl_sync(0xffffffffu, score, best_e & 31);
+    if (score == -INFINITY) score = 0.f;
+    if (lane == j) { chosen_w = score; chosen_e = best_e; }
+    total += score;
   }
   if (lane < top) {
     choice[(size_t)t * top + lane] = chosen_e;
-    weight[(size_t)t * top + lane] = renormalize ? chosen_w / total : chosen_w;
+    weight[(size_t)t * top + lane] = (renormalize ? chosen_w / (total + renorm_eps) : chosen_w) * out_scale;
   }
 }
 
@@ -196,16 +243,22 @@ ILB_EXPORT int ilb_moe_max_experts() { return 32 * kMaxExpertsPerLane; }
 ILB_EXPORT int ilb_moe_max_top() { return kMaxTop; }
 
 // logits: [T, ld] 32-bit, the first `experts` columns are the router's.  choice / weight: [T, top].
-// bias: [experts] added to the logits first, or null.
+// bias: [experts] added to the logits first, or null.  correction: [experts] added to the scores for the ranking
+// alone, or null.  groups > 1 with keep < groups: only the best `keep` of `groups` equal groups of neighbouring
+// experts can be chosen.  Weights: the chosen scores (divided by their sum + renorm_eps when renormalize) * out_scale.
 ILB_EXPORT int ilb_moe_route(const float* logits, const float* bias, int ld, int n_tokens, int experts, int top, int softmax,
-                             int renormalize, int* choice, float* weight, cudaStream_t stream) {
+                             int renormalize, int* choice, float* weight, const float* correction, int groups, int keep,
+                             float out_scale, float renorm_eps, cudaStream_t stream) {
+  ILB_REQUIRE(groups >= 1 && groups <= 32 && experts % groups == 0 && keep >= 1 && keep <= groups,
+              "moe_route: %d groups (at most 32, dividing %d experts), %d kept", groups, experts, keep);
+  ILB_REQUIRE(top <= (experts / groups) * keep, "moe_route: top %d exceeds the %d experts of the kept groups", top, (experts / groups) * keep);
   ILB_REQUIRE(n_tokens >= 0 && experts > 0 && experts <= 32 * kMaxExpertsPerLane, "moe_route: %d experts (at most %d)", experts,
               32 * kMaxExpertsPerLane);
   ILB_REQUIRE(top > 0 && top <= experts && top <= kMaxTop, "moe_route: top %d of %d experts (at most %d)", top, experts, kMaxTop);
   ILB_REQUIRE(ld >= experts, "moe_route: row stride too small");
   if (n_tokens == 0) return 0;
   ilb::launch(moe_route_kernel, dim3((n_tokens + 3) / 4), dim3(128), 0, stream, logits, bias, ld, n_tokens, experts, top, softmax,
-              renormalize, choice, weight);
+              renormalize, choice, weight, correction, groups, keep, out_scale, renorm_eps);
   return check_launch("moe_route");
 }
 

@@ -178,9 +178,12 @@ SSM_CHUNK_FROM = 128       # portions from this many tokens on are cut into chun
 
 
 def ssm_conv(proj: torch.Tensor, col0: int, channels: int, weight: torch.Tensor, bias: torch.Tensor, state: torch.Tensor,
-             step, out: torch.Tensor) -> None:
+             step, out: torch.Tensor, activation: str = "silu") -> None:
     """out[t, c] = silu(bias[c] + sum_k weight[c, k] * raw[t - (taps - 1) + k, c]) over columns col0 .. of `proj`; the raw
-    inputs ahead of the step come from state [slots, taps - 1, channels], which is brought up to date."""
+    inputs ahead of the step come from state [slots, taps - 1, channels], which is brought up to date.  `activation`
+    "none" leaves the sum as it is."""
+    if activation not in ("silu", "none"):
+        raise KernelError(f"ssm_conv: unknown activation {activation!r}")
     _need(proj, "ssm projection"); _need(weight, "conv weight", torch.float32); _need(bias, "conv bias", torch.float32)
     _need(state, "conv state", torch.float32); _need(out, "conv out", torch.float32)
     T, taps = proj.shape[0], weight.shape[1]
@@ -189,20 +192,25 @@ def ssm_conv(proj: torch.Tensor, col0: int, channels: int, weight: torch.Tensor,
         raise KernelError("ssm_conv: shapes do not agree")
     n_tiles = sum(-(-n // SSM_CONV_TILE) for n in step.h_q_len) + (step.n_seqs - len(step.h_q_len))
     _call("ssm", "ilb_ssm_conv", _ptr(proj), _i(_code(proj)), _i(proj.stride(0)), _i(col0), _i(channels), _i(taps), _ptr(weight),
-          _ptr(bias), _ptr(state), _ptr(step.cu_q), _ptr(step.slots), _i(step.n_seqs), _i(n_tiles), _ptr(out), _stream(out))
+          _ptr(bias), _ptr(state), _ptr(step.cu_q), _ptr(step.slots), _i(step.n_seqs), _i(n_tiles), _ptr(out),
+          _i(1 if activation == "silu" else 0), _stream(out))
 
 
-def ssm_scan(act: torch.Tensor, proj: torch.Tensor, dt_col0: int, dt_bias: torch.Tensor, a_log: torch.Tensor, skip: torch.Tensor,
-             state: torch.Tensor, y: torch.Tensor, step, heads: int, head_dim: int, n_state: int, groups: int,
-             workspace=None, chunk: Optional[int] = None) -> None:
+def ssm_scan(act: torch.Tensor, proj: Optional[torch.Tensor], dt_col0: int, dt_bias: Optional[torch.Tensor], a_log: torch.Tensor,
+             skip: Optional[torch.Tensor], state: torch.Tensor, y: torch.Tensor, step, heads: int, head_dim: int, n_state: int,
+             groups: int, workspace=None, chunk: Optional[int] = None, fixed_decay: bool = False) -> None:
     """The recurrence S_t = exp(-exp(a_log) d_t) S_{t-1} + d_t B_t u_t^T, y_t = S_t^T C_t + skip * u_t per head over the
     step's tokens, from and to state [slots, heads, n_state, head_dim] (see ssm.cu).  `chunk`: None picks by the
-    longest portion; 0 runs every sequence in one go; n cuts portions into chunks of n tokens."""
+    longest portion; 0 runs every sequence in one go; n cuts portions into chunks of n tokens.  `fixed_decay`: every
+    step size is one and `a_log` holds each head's decay itself (S_t = decay S_{t-1} + B_t u_t^T, y_t = S_t^T C_t);
+    `proj`, `dt_bias` and `skip` are None then."""
     _need(act, "ssm activations", torch.float32); _need(proj, "ssm projection"); _need(state, "ssm state", torch.float32)
     _need(y, "ssm y", torch.float32)
+    if fixed_decay != (proj is None) or fixed_decay != (dt_bias is None) or fixed_decay != (skip is None):
+        raise KernelError("ssm_scan: a fixed decay takes no step sizes, and step sizes no fixed decay")
     for t, w in ((dt_bias, "dt bias"), (a_log, "decay logarithms"), (skip, "skip weights")):
         _need(t, "ssm " + w, torch.float32)
-        if t.numel() != heads:
+        if t is not None and t.numel() != heads:
             raise KernelError("ssm_scan: one " + w + " per head")
     T, channels = act.shape
     if channels != heads * head_dim + 2 * groups * n_state or tuple(y.shape) != (T, heads * head_dim) \
@@ -225,9 +233,10 @@ def ssm_scan(act: torch.Tensor, proj: torch.Tensor, dt_col0: int, dt_bias: torch
         n_blocks = sum(-(-n // chunk) for n in step.h_q_len) + (step.n_seqs - len(step.h_q_len))
         chunk_state = workspace.buffer("ssm.chunk_state", (n_blocks, heads, n_state, head_dim), torch.float32)
         chunk_decay = workspace.buffer("ssm.chunk_decay", (n_blocks, heads), torch.float32)
-    _call("ssm", "ilb_ssm_scan", _ptr(act), _ptr(proj), _i(_code(proj)), _i(proj.stride(0)), _i(dt_col0), _i(channels), _ptr(dt_bias),
+    _call("ssm", "ilb_ssm_scan", _ptr(act), _ptr(proj), _i(F32 if proj is None else _code(proj)), _i(0 if proj is None else proj.stride(0)),
+          _i(dt_col0), _i(channels), _ptr(dt_bias),
           _ptr(a_log), _ptr(skip), _ptr(state), _ptr(chunk_state), _ptr(chunk_decay), _ptr(y), _ptr(step.cu_q), _ptr(step.slots),
-          _i(step.n_seqs), _i(heads), _i(head_dim), _i(n_state), _i(groups), _i(chunk), _i(n_blocks), _stream(y))
+          _i(step.n_seqs), _i(heads), _i(head_dim), _i(n_state), _i(groups), _i(chunk), _i(n_blocks), _i(1 if fixed_decay else 0), _stream(y))
 
 
 def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, groups: int, out: torch.Tensor) -> None:
@@ -342,6 +351,105 @@ def group_norm_add(y: torch.Tensor, weight: torch.Tensor, eps: float, groups: in
           _ptr(x), _ptr(out), _i(F32 if out is None else _code(out)), _i(1 if zero else 0), _stream(y))
 
 
+def dyt(x: torch.Tensor, alpha: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, out: torch.Tensor) -> None:
+    """out = tanh(alpha * x) * weight + bias, element by element (alpha one stored number); x 32-bit, out of any dtype
+    and possibly x itself."""
+    _need(x, "dyt x", torch.float32); _need(alpha, "dyt alpha", torch.float32); _need(weight, "dyt weight", torch.float32)
+    _need(bias, "dyt bias", torch.float32); _need(out, "dyt out")
+    width = x.shape[-1]
+    if alpha.numel() != 1 or weight.numel() != width or bias.numel() != width or out.shape != x.shape:
+        raise KernelError("dyt: shapes do not agree")
+    _call("sublayer_norm", "ilb_dyt", _ptr(x), _ptr(alpha), _ptr(weight), _ptr(bias), _ptr(out), _i(_code(out)), _i(x.numel() // width),
+          _i(width), _stream(x))
+
+
+def dyt_add(y: torch.Tensor, norm, mult: float, x: torch.Tensor, next_norm=None, out: Optional[torch.Tensor] = None,
+            zero: bool = False) -> None:
+    """x += mult * (tanh(a y) g + b) with (a, g, b) = `norm`; then, with `next_norm` and `out`, out = tanh(a2 x) g2 + b2 in
+    out's dtype; `zero` leaves y at zero.  y and x are 32-bit and of one shape."""
+    _need(y, "dyt_add y", torch.float32); _need(x, "dyt_add x", torch.float32); _need(out, "dyt_add out")
+    width = x.shape[-1]
+    if y.shape != x.shape or (out is not None and out.shape != x.shape) or (out is None) != (next_norm is None):
+        raise KernelError("dyt_add: shapes do not agree")
+    for n in (norm, next_norm):
+        if n is not None:
+            a, g, b = n
+            _need(a, "dyt alpha", torch.float32); _need(g, "dyt weight", torch.float32); _need(b, "dyt bias", torch.float32)
+            if a.numel() != 1 or g.numel() != width or b.numel() != width:
+                raise KernelError("dyt_add: a norm's tensors do not fit the row")
+    a2, g2, b2 = next_norm if next_norm is not None else (None, None, None)
+    _call("sublayer_norm", "ilb_dyt_add", _ptr(y), _ptr(norm[0]), _ptr(norm[1]), _ptr(norm[2]), _f(mult), _ptr(x), _ptr(a2), _ptr(g2),
+          _ptr(b2), _ptr(out), _i(F32 if out is None else _code(out)), _i(1 if zero else 0), _i(x.numel() // width), _i(width), _stream(x))
+
+
+# --------------------------------------------------------------------------- linear recurrences over channels, gates
+LRU_CHUNK = 64             # tokens per chunk when a long portion's recurrence runs chunks side by side
+LRU_CHUNK_FROM = 128       # portions from this many tokens on are cut into chunks
+
+
+def lru_scan(gates: torch.Tensor, u: torch.Tensor, proj: torch.Tensor, y_col0: int, r_bias: torch.Tensor, i_bias: torch.Tensor,
+             lam: torch.Tensor, rate: float, state: torch.Tensor, out: torch.Tensor, step, block_width: int, workspace=None,
+             chunk: Optional[int] = None) -> None:
+    """The gated linear recurrence over channels (see recurrent.cu): gates [T, 2 W] 32-bit (per block of `block_width`
+    channels its r logits, then its i logits), u [T, W] 32-bit, the raw output branch at columns y_col0 .. of `proj`;
+    from and to state [slots, W]; out [T, W] = S * gelu_tanh(y) in proj's dtype.  `chunk`: None picks by the longest
+    portion; 0 runs every sequence in one go; n cuts portions into chunks of n tokens."""
+    _need(gates, "lru gates", torch.float32, contiguous=False); _need(u, "lru input", torch.float32); _need(proj, "lru projection", contiguous=False)
+    _need(state, "lru state", torch.float32); _need(out, "lru out", proj.dtype)
+    T, W = u.shape
+    for t, w in ((r_bias, "r bias"), (i_bias, "i bias"), (lam, "decay parameter")):
+        _need(t, "lru " + w, torch.float32)
+        if t.numel() != W:
+            raise KernelError("lru_scan: one " + w + " per channel")
+    if gates.shape[0] != T or gates.shape[1] < 2 * W or gates.stride(1) != 1 or proj.shape[0] != T or proj.stride(1) != 1 \
+            or tuple(out.shape) != (T, W) or tuple(state.shape[1:]) != (W,) or W % block_width:
+        raise KernelError("lru_scan: shapes do not agree")
+    if chunk is None:
+        chunk = LRU_CHUNK if step.max_q_len >= LRU_CHUNK_FROM else 0
+    chunk_state = chunk_decay = None
+    n_blocks = step.n_seqs
+    if chunk:
+        if workspace is None:
+            raise KernelError("lru_scan: chunks need a workspace")
+        n_blocks = sum(-(-n // chunk) for n in step.h_q_len) + (step.n_seqs - len(step.h_q_len))
+        chunk_state = workspace.buffer("lru.chunk_state", (n_blocks, W), torch.float32)
+        chunk_decay = workspace.buffer("lru.chunk_decay", (n_blocks, W), torch.float32)
+    _call("recurrent", "ilb_lru_scan", _ptr(gates), _i(gates.stride(0)), _ptr(u), _ptr(proj), _i(_code(proj)), _i(proj.stride(0)), _i(y_col0),
+          _ptr(r_bias), _ptr(i_bias), _ptr(lam), _f(rate), _ptr(state), _ptr(chunk_state), _ptr(chunk_decay), _ptr(out), _ptr(step.cu_q),
+          _ptr(step.slots), _i(step.n_seqs), _i(W), _i(block_width), _i(chunk), _i(n_blocks), _stream(out))
+
+
+def silu_rows(x: torch.Tensor, width: int, out: torch.Tensor) -> None:
+    """out[t, :width] = silu(x[t, :width]) in 32-bit; x may have more columns."""
+    _need(x, "silu_rows x", contiguous=False); _need(out, "silu_rows out", torch.float32)
+    if x.stride(1) != 1 or x.shape[1] < width or tuple(out.shape) != (x.shape[0], width):
+        raise KernelError("silu_rows: shapes do not agree")
+    _call("recurrent", "ilb_silu_rows", _ptr(x), _i(_code(x)), _i(x.stride(0)), _ptr(out), _i(x.shape[0]), _i(width), _stream(out))
+
+
+def rms_gate(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out = y / sqrt(mean(y^2) + eps) * weight * sigmoid(gate) * scale over whole rows; y 32-bit, gate [T, >= width]
+    (its first `width` columns) and out in the compute dtype."""
+    _need(y, "rms_gate y", torch.float32); _need(gate, "rms_gate gate", contiguous=False); _need(weight, "rms_gate weight", torch.float32)
+    _need(out, "rms_gate out", gate.dtype)
+    T, width = y.shape
+    if gate.shape[0] != T or gate.shape[1] < width or gate.stride(1) != 1 or weight.numel() != width or out.shape != y.shape:
+        raise KernelError("rms_gate: shapes do not agree")
+    _call("recurrent", "ilb_rms_gate", _ptr(y), _ptr(gate), _i(_code(gate)), _i(gate.stride(0)), _ptr(weight), _ptr(out), _i(T), _i(width),
+          _f(eps), _f(scale), _stream(out))
+
+
+def head_gate(o: torch.Tensor, gate: torch.Tensor, heads: int, scale: float = 1.0) -> None:
+    """o[t, h, :] *= sigmoid(gate[t, h]) * scale in place; o [T, heads * dv], gate [T, >= heads] (its first `heads`
+    columns), both in the compute dtype."""
+    _need(o, "head_gate o"); _need(gate, "head_gate gate", o.dtype, contiguous=False)
+    T, width = o.shape
+    if width % heads or gate.shape[0] != T or gate.shape[1] < heads or gate.stride(1) != 1:
+        raise KernelError("head_gate: shapes do not agree")
+    _call("recurrent", "ilb_head_gate", _ptr(o), _ptr(gate), _i(_code(o)), _i(gate.stride(0)), _i(T), _i(heads), _i(width // heads),
+          _f(scale), _stream(o))
+
+
 def gated_rows(a: torch.Tensor, table: torch.Tensor, col0: int, tokens: torch.Tensor, out: torch.Tensor) -> None:
     """out[t, k] = gelu_tanh(a[t, k]) * table[tokens[t], col0 + k]."""
     _need(a, "gated_rows a"); _need(table, "gated_rows table", a.dtype); _need(out, "gated_rows out", a.dtype)
@@ -416,16 +524,23 @@ def moe_logits(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 
 
 def moe_route(logits: torch.Tensor, experts: int, top: int, softmax: bool, renormalize: bool,
-              choice: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
+              choice: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+              correction: Optional[torch.Tensor] = None, groups: int = 1, keep: int = 1, scale: float = 1.0,
+              renorm_eps: float = 0.0) -> None:
     """The `top` experts with the largest scores of every token and their weights; `bias` [experts]
-    is added to the logits first."""
+    is added to the logits first.  `correction` [experts] is added to the scores for the ranking alone (the
+    weights stay the scores); with `groups` > 1 the experts form that many equal groups of neighbours, a group
+    ranks by its best member, and only the best `keep` groups' experts can be chosen.  The weights are divided by
+    their sum + `renorm_eps` when `renormalize`, then multiplied by `scale`."""
     _need(logits, "router logits", torch.float32); _need(choice, "moe choice", torch.int32); _need(weight, "moe weight", torch.float32)
-    _need(bias, "router bias", torch.float32)
+    _need(bias, "router bias", torch.float32); _need(correction, "router correction", torch.float32)
     T = logits.shape[0]
-    if choice.numel() != T * top or weight.numel() != T * top or logits.shape[1] < experts or (bias is not None and bias.numel() != experts):
+    if choice.numel() != T * top or weight.numel() != T * top or logits.shape[1] < experts or (bias is not None and bias.numel() != experts) \
+            or (correction is not None and correction.numel() != experts):
         raise KernelError("moe_route: shapes do not agree")
     _call("moe", "ilb_moe_route", _ptr(logits), _ptr(bias), _i(logits.stride(0)), _i(T), _i(experts), _i(top), _i(1 if softmax else 0),
-          _i(1 if renormalize else 0), _ptr(choice), _ptr(weight), _stream(logits))
+          _i(1 if renormalize else 0), _ptr(choice), _ptr(weight), _ptr(correction), _i(groups), _i(keep), _f(scale), _f(renorm_eps),
+          _stream(logits))
 
 
 def moe_plan(choice: torch.Tensor, experts: int, block_rows: int, pos: torch.Tensor, block_expert: torch.Tensor) -> None:
@@ -797,12 +912,14 @@ def gemm_tc_eligible(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> boo
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
-            accumulate: bool = False, max_ctas: int = 0, swiglu: bool = False, gate: str = "silu") -> None:
+            accumulate: bool = False, max_ctas: int = 0, swiglu: bool = False, gate: str = "silu", glu=None) -> None:
     """out (+)= a @ w.T (+ bias) on tcgen05 tensor cores (see gemm_tcgen05.cu).  With
     `swiglu`, `w` holds blocks of 64 gate rows followed by their 64 up rows and `out` is
     [M, N/2] = act(gate) * up, act = `gate` ("silu" or "relu")."""
     if gate not in ("silu", "relu"):
         raise KernelError(f"gemm: the gated epilogue has no activation {gate!r}")
+    if glu is not None:
+        raise KernelError("gemm: the clamped gated unit is not in this product's epilogue")
     _need(a, "gemm a", torch.bfloat16); _need(w, "gemm w", torch.bfloat16); _need(out, "gemm out")
     _need(bias, "gemm bias", torch.float32)
     M, K = a.shape

@@ -14,7 +14,9 @@
 //            zero state, giving its own contribution and the product of its decays; (2) the chunks'
 //            incoming states, one after the other (a handful of fused multiply-adds per element);
 //            (3) every chunk again from its incoming state, writing y.  Short portions and single
-//            tokens run pass (3) alone, from and to the state slot.
+//            tokens run pass (3) alone, from and to the state slot.  `fixed`: every step size is one and a head's
+//            decay is a stored constant, S_t = decay_h S_{t-1} + B_t u_t^T, y_t = S_t^T C_t (a linear attention whose
+//            keys are B, queries C and values u).
 //   gate     out[t, :] = rms_group(y[t, :] * silu(z[t, :])) * w, each of `groups` equal parts of a row
 //            divided by its own root mean square.
 //
@@ -49,7 +51,7 @@ template <typename TI, int MT>
 __global__ void __launch_bounds__(128)
 ssm_conv_kernel(const TI* __restrict__ proj, int ld, int col0, int channels, int taps, const float* __restrict__ w,
                 const float* __restrict__ bias, float* __restrict__ state, const int* __restrict__ cu_q,
-                const int* __restrict__ slots, int n_seqs, float* __restrict__ out) {
+                const int* __restrict__ slots, int n_seqs, float* __restrict__ out, int activation) {
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();
   int seq, tile;
@@ -85,7 +87,7 @@ ssm_conv_kernel(const TI* __restrict__ proj, int ld, int col0, int channels, int
 #pragma unroll
     for (int k = 0; k < MT - 1; ++k) acc = fmaf(wr[k], hist[k], acc);
     acc = fmaf(wr[MT - 1], x, acc);
-    out[(size_t)(tok0 + lt) * channels + c] = silu_f(acc);
+    out[(size_t)(tok0 + lt) * channels + c] = activation ? silu_f(acc) : acc;
 #pragma unroll
     for (int k = 0; k + 1 < MT - 1; ++k) hist[k] = hist[k + 1];
     if (MT > 1) hist[MT - 2] = x;
@@ -107,16 +109,16 @@ ssm_conv_kernel(const TI* __restrict__ proj, int ld, int col0, int channels, int
 
 // proj: [T, ld] of `dtype`, the raw channels at columns col0 .. col0 + channels - 1; w: [channels, taps];
 // state: [slots, taps - 1, channels]; out: [T, channels] 32-bit; n_tiles = sum over the sequences of
-// ceil(tokens / 16).
+// ceil(tokens / 16).  activation: 1 = silu on the sum, 0 = the sum as it is.
 ILB_EXPORT int ilb_ssm_conv(const void* proj, int dtype, int ld, int col0, int channels, int taps, const float* w,
                             const float* bias, float* state, const int* cu_q, const int* slots, int n_seqs, int n_tiles,
-                            float* out, cudaStream_t stream) {
+                            float* out, int activation, cudaStream_t stream) {
   ILB_REQUIRE(channels > 0 && taps >= 1 && taps <= kMaxTaps, "ssm_conv: %d channels, %d taps (at most %d)", channels, taps, kMaxTaps);
   ILB_REQUIRE(n_seqs >= 0 && n_tiles >= 0 && ld >= col0 + channels, "ssm_conv: bad sizes");
   if (n_tiles == 0) return 0;
   const dim3 grid(n_tiles, (channels + 127) / 128);
 #define ILB_CONV(TI, MT) ilb::launch(ssm_conv_kernel<TI, MT>, grid, dim3(128), 0, stream, (const TI*)proj, ld, col0, channels, taps, \
-                                      w, bias, state, cu_q, slots, n_seqs, out)
+                                      w, bias, state, cu_q, slots, n_seqs, out, activation)
   if (dtype == kF32) { if (taps <= 4) ILB_CONV(float, 4); else ILB_CONV(float, kMaxTaps); }
   else if (dtype == kBF16) { if (taps <= 4) ILB_CONV(__nv_bfloat16, 4); else ILB_CONV(__nv_bfloat16, kMaxTaps); }
   else return fail("ssm_conv: unknown dtype %d", dtype);
@@ -135,6 +137,7 @@ struct ScanParams {
   float* y;                // [T, heads * P]
   const int* cu_q; const int* slots;
   int n_seqs, ld, dt_col0, channels, heads, P, N, groups, chunk, pass;
+  int fixed;               // 1: a_log holds every head's decay itself and every step size is one (no proj, no dt_bias)
 };
 
 enum : int { kPassWhole = 0, kPassLocal = 1, kPassFinal = 3 };
@@ -178,7 +181,10 @@ ssm_scan_kernel(const ScanParams p) {
   const int begin = tok0 + ci * p.chunk, end = tok0 + min(q_len, (ci + 1) * p.chunk);
   const int slot = p.slots[seq];
   const int inner = p.heads * p.P;
-  const float rate = -expf(p.a_log[h]), bias = p.dt_bias[h], skip = p.skip[h];
+  // fixed: S_t = decay S_{t-1} + B_t u_t^T with the decay as stored; rate is the logarithm of a step's decay either way
+  const float fixed_decay = p.fixed ? p.a_log[h] : 0.f;
+  const float rate = p.fixed ? logf(fixed_decay) : -expf(p.a_log[h]);
+  const float bias = p.fixed ? 0.f : p.dt_bias[h], skip = p.skip != nullptr ? p.skip[h] : 0.f;
   const size_t per_head = (size_t)p.N * p.P;
 
   float S[NPER];
@@ -226,6 +232,7 @@ ssm_scan_kernel(const ScanParams p) {
     cp_async_commit_group();
   };
   auto raw_step = [&](int t0n) {
+    if (p.fixed) return 0.f;
     return tid < min(kScanTokens, end - t0n) ? to_float(reinterpret_cast<const TI*>(p.proj)[(size_t)(t0n + tid) * p.ld + p.dt_col0 + h]) : 0.f;
   };
   float decay_all = 1.f;
@@ -240,9 +247,9 @@ ssm_scan_kernel(const ScanParams p) {
     float* dsb = ds + buf * kScanTokens;
     float* asb = as + buf * (kScanTokens + 4);
     if (tid < ts) {
-      const float d = softplus_f(raw + bias);
+      const float d = p.fixed ? 1.f : softplus_f(raw + bias);
       dsb[tid] = d;
-      asb[tid] = LOCAL ? rate * d : expf(rate * d);
+      asb[tid] = LOCAL ? rate * d : (p.fixed ? fixed_decay : expf(rate * d));
     }
     if (t0 + kScanTokens < end) {
       raw = raw_step(t0 + kScanTokens);
@@ -390,18 +397,20 @@ static int scan_launch(const ScanParams& p, int n_blocks, cudaStream_t stream) {
 ILB_EXPORT int ilb_ssm_scan(const float* act, const void* proj, int dtype, int ld, int dt_col0, int channels,
                             const float* dt_bias, const float* a_log, const float* skip, float* state, float* chunk_state,
                             float* chunk_decay, float* y, const int* cu_q, const int* slots, int n_seqs, int heads, int P, int N,
-                            int groups, int chunk, int n_blocks, cudaStream_t stream) {
+                            int groups, int chunk, int n_blocks, int fixed, cudaStream_t stream) {
   ILB_REQUIRE(heads > 0 && P > 0 && N > 0 && groups > 0 && heads % groups == 0, "ssm_scan: bad sizes");
   ILB_REQUIRE(channels == heads * P + 2 * groups * N, "ssm_scan: %d channels for %d heads of %d, %d groups of %d", channels, heads, P, groups, N);
   ILB_REQUIRE(heads <= 65535 && n_seqs <= 65535, "ssm_scan: too many heads or sequences");
   ILB_REQUIRE(dtype == kF32 || dtype == kBF16, "ssm_scan: unknown dtype %d", dtype);
+  ILB_REQUIRE(fixed ? a_log != nullptr : (proj != nullptr && dt_bias != nullptr && a_log != nullptr && skip != nullptr),
+              "ssm_scan: missing inputs");
   ILB_REQUIRE(chunk >= 0 && (chunk == 0 || (chunk_state != nullptr && chunk_decay != nullptr)), "ssm_scan: chunks need their scratch");
   if (n_blocks <= 0 || n_seqs <= 0) return 0;
   ScanParams p;
   p.act = act; p.proj = proj; p.dt_bias = dt_bias; p.a_log = a_log; p.skip = skip; p.state = state;
   p.chunk_state = chunk_state; p.chunk_decay = chunk_decay; p.y = y; p.cu_q = cu_q; p.slots = slots;
   p.n_seqs = n_seqs; p.ld = ld; p.dt_col0 = dt_col0; p.channels = channels; p.heads = heads; p.P = P; p.N = N;
-  p.groups = groups;
+  p.groups = groups; p.fixed = fixed ? 1 : 0;
   auto run = [&](int pass) {
     p.pass = pass;
     return dtype == kF32 ? scan_launch<float>(p, n_blocks, stream) : scan_launch<__nv_bfloat16>(p, n_blocks, stream);

@@ -199,4 +199,76 @@ ILB_EXPORT int ilb_gated_rows(const void* a, const void* table, int dtype, int l
   return check_launch("gated_rows");
 }
 
+// ---------------------------------------------------------------- the norm without statistics
+// dyt(x) = tanh(alpha x) g + b, element by element: alpha one stored number, g and b vectors over the row.
+//   dyt        out = dyt(x)                                                  (x 32-bit, out any dtype; out may be x)
+//   dyt_add    x += mult * dyt1(y);  then, if asked, out = dyt2(x) in the compute dtype (what the next sublayer
+//              reads) and y = 0 (what it adds into): the norm on a sublayer's output, the residual sum and the
+//              norm in front of the next sublayer as one launch.
+struct DytWeights { const float* alpha; const float* g; const float* b; };
+
+template <typename TO>
+__global__ void __launch_bounds__(kNormThreads)
+dyt_kernel(const float* __restrict__ x, DytWeights n, TO* __restrict__ out, size_t total, int width) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  const float alpha = n.alpha[0];
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % width);
+    out[i] = from_float<TO>(fmaf(tanhf(alpha * x[i]), n.g[c], n.b[c]));
+  }
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(kNormThreads)
+dyt_add_kernel(float* __restrict__ y, DytWeights n1, float mult, float* __restrict__ x, DytWeights n2, TO* __restrict__ out,
+               int zero, size_t total, int width) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  const float a1 = n1.alpha[0], a2 = out != nullptr ? n2.alpha[0] : 0.f;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % width);
+    const float v = fmaf(mult, fmaf(tanhf(a1 * y[i]), n1.g[c], n1.b[c]), x[i]);
+    x[i] = v;
+    if (out != nullptr) out[i] = from_float<TO>(fmaf(tanhf(a2 * v), n2.g[c], n2.b[c]));
+    if (zero) y[i] = 0.f;
+  }
+}
+
+static inline int dyt_blocks(size_t total) {
+  const size_t want = (total + kNormThreads - 1) / kNormThreads;
+  return (int)(want < 148 * 16 ? want : 148 * 16);
+}
+
+ILB_EXPORT int ilb_dyt(const float* x, const float* alpha, const float* g, const float* b, void* out, int out_dtype, int rows,
+                       int width, cudaStream_t stream) {
+  ILB_REQUIRE(rows >= 0 && width > 0, "dyt: bad sizes");
+  if (rows == 0) return 0;
+  const size_t total = (size_t)rows * width;
+  const DytWeights n{alpha, g, b};
+  if (out_dtype == kF32) ilb::launch(dyt_kernel<float>, dim3(dyt_blocks(total)), dim3(kNormThreads), 0, stream, x, n, (float*)out, total, width);
+  else if (out_dtype == kBF16)
+    ilb::launch(dyt_kernel<__nv_bfloat16>, dim3(dyt_blocks(total)), dim3(kNormThreads), 0, stream, x, n, (__nv_bfloat16*)out, total, width);
+  else return fail("dyt: unknown dtype %d", out_dtype);
+  return check_launch("dyt");
+}
+
+// y, x: [rows, width] 32-bit; out: [rows, width] of `out_dtype` or null (then alpha2, g2, b2 are not read).
+ILB_EXPORT int ilb_dyt_add(float* y, const float* alpha1, const float* g1, const float* b1, float mult, float* x,
+                           const float* alpha2, const float* g2, const float* b2, void* out, int out_dtype, int zero, int rows,
+                           int width, cudaStream_t stream) {
+  ILB_REQUIRE(rows >= 0 && width > 0, "dyt_add: bad sizes");
+  ILB_REQUIRE(out == nullptr || (alpha2 != nullptr && g2 != nullptr && b2 != nullptr), "dyt_add: the second norm's tensors are missing");
+  if (rows == 0) return 0;
+  const size_t total = (size_t)rows * width;
+  const DytWeights n1{alpha1, g1, b1}, n2{alpha2, g2, b2};
+  if (out == nullptr || out_dtype == kF32)
+    ilb::launch(dyt_add_kernel<float>, dim3(dyt_blocks(total)), dim3(kNormThreads), 0, stream, y, n1, mult, x, n2, (float*)out, zero, total, width);
+  else if (out_dtype == kBF16)
+    ilb::launch(dyt_add_kernel<__nv_bfloat16>, dim3(dyt_blocks(total)), dim3(kNormThreads), 0, stream, y, n1, mult, x, n2,
+                (__nv_bfloat16*)out, zero, total, width);
+  else return fail("dyt_add: unknown dtype %d", out_dtype);
+  return check_launch("dyt_add");
+}
+
 ILB_DEFINE_LAST_ERROR()

@@ -28,6 +28,10 @@ csrc/attention_mix.cu): `query_temperature` = (coef, every): q at position i is 
 1 + coef ln(floor((i + 1) / every) + 1); `softcap` = c: s <- c tanh(s / c); `distance_bias`: s <- s -
 r1_h ln(1 + r2_h (i - j)) with two learned vectors; `head_mix`: s_h <- sum_g M[h, g] s_g with a learned
 [heads, heads] matrix; in that order.  `sink`: a learned logit per head joins the softmax's denominator.
+
+`output_gate` = "head": head h's output is multiplied by sigmoid((W_g x)_h), one number a head from a matrix
+[heads, hidden] whose rows ride behind q|k|v in the one projection.  `out_scale`: a constant on the whole mixer's
+output (a mixer that runs beside another one), applied in 32-bit to what the output projection reads and to its bias.
 """
 from __future__ import annotations
 
@@ -86,6 +90,13 @@ class GQAttention(Mixer):
         self.distance_bias = bool(spec.get("distance_bias", False))
         self.head_mix = bool(spec.get("head_mix", False))
         self.has_sink = bool(spec.get("sink", False))
+        self.output_gate = spec.get("output_gate")
+        if self.output_gate not in (None, "head"):
+            raise ValueError(f"output_gate must be None or 'head', found {self.output_gate!r}")
+        self.out_scale = float(spec.get("out_scale", 1.0))
+        if self.out_scale != 1.0 and not self.output_gate:
+            raise ValueError("attention: a constant on the output is applied by the gate's kernel (output_gate)")
+        self.gate_rows = -(-self.nq // 8) * 8 if self.output_gate else 0      # (padded: the projection's rows stay multiples of 16 bytes)
         self.shaped = bool(self.temp_coef or self.softcap or self.distance_bias or self.head_mix)
         if self.shaped and self.value_mix is not None:
             raise ValueError("attention: reshaped scores and mixed values are not served together")
@@ -95,7 +106,7 @@ class GQAttention(Mixer):
         names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
                  "qb": "q_proj.bias", "kb": "k_proj.bias", "vb": "v_proj.bias", "ob": "o_proj.bias",
                  "qn": "q_norm.weight", "kn": "k_norm.weight", "vmix": "v_mix",
-                 "r1": "r1", "r2": "r2", "head_mix": "talk", "sink": "sink"}
+                 "r1": "r1", "r2": "r2", "head_mix": "talk", "sink": "sink", "g": "gate.weight"}
         for role, name in spec.get("names", ()):
             if role not in names:
                 raise ValueError(f"attention has no tensor role {role!r}")
@@ -127,6 +138,8 @@ class GQAttention(Mixer):
             out.append(WeightDecl(n["head_mix"], (self.nq, self.nq), "vector", "eye"))
         if self.has_sink:
             out.append(WeightDecl(n["sink"], (self.nq,), "vector", "around_zero"))
+        if self.output_gate:
+            out.append(WeightDecl(n["g"], (self.nq, H)))
         if self.value_mix == "mixed":
             out.append(WeightDecl(n["vmix"], (), "vector", "mix"))
         elif bool(self.spec.get("value_mix_tensor_unused", False)):
@@ -135,12 +148,19 @@ class GQAttention(Mixer):
 
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         n = self.names
-        self.w_qkv = torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]], dim=0).contiguous()
+        rows = [tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]]
+        if self.output_gate:
+            g = tensors[n["g"]]
+            rows += [g, g.new_zeros(self.gate_rows - self.nq, self.hidden)]
+        self.w_qkv = torch.cat(rows, dim=0).contiguous()
         self.w_o = tensors[n["o"]].contiguous()
         if self.bias:
-            self.b_qkv = torch.cat([tensors[n["qb"]], tensors[n["kb"]], tensors[n["vb"]]]).contiguous()
+            biases = [tensors[n["qb"]], tensors[n["kb"]], tensors[n["vb"]]]
+            if self.output_gate:
+                biases.append(biases[0].new_zeros(self.gate_rows))
+            self.b_qkv = torch.cat(biases).contiguous()
         if self.out_bias:
-            self.b_o = tensors[n["ob"]].contiguous()
+            self.b_o = (tensors[n["ob"]] * self.out_scale).contiguous() if self.out_scale != 1.0 else tensors[n["ob"]].contiguous()
         if self.value_mix == "mixed":
             self.v_lambda = tensors[n["vmix"]].reshape(1).contiguous()
         if self.qk_norm:
@@ -158,7 +178,7 @@ class GQAttention(Mixer):
 
     def scratch_bytes(self, tokens: int) -> int:
         size = torch.empty((), dtype=self.ctx.dtype).element_size()
-        width = (self.nq + self.nkv) * self.d + self.nkv * self.dv
+        width = (self.nq + self.nkv) * self.d + self.nkv * self.dv + self.gate_rows
         kept = self.nkv * self.dv if self.value_mix else 0
         return tokens * ((width + self.nq * (self.d + self.dv) + kept) * size + self.rotary_dim * 4)
 
@@ -166,7 +186,8 @@ class GQAttention(Mixer):
     def forward(self, x: torch.Tensor, residual: torch.Tensor, step, cache) -> None:
         T = x.shape[0]
         ws, dt = self.ctx.workspace, self.ctx.dtype
-        width = (self.nq + self.nkv) * self.d + self.nkv * self.dv
+        gate_col0 = (self.nq + self.nkv) * self.d + self.nkv * self.dv      # the heads' gate logits ride behind q | k | v
+        width = gate_col0 + self.gate_rows
         qkv = ws.buffer("attn.qkv", (T, width), dt)
         ops.scope("attention.qkv_projection")
         linear(x, self.w_qkv, qkv, self.b_qkv)
@@ -193,6 +214,7 @@ class GQAttention(Mixer):
                                        rotary_dim=self.rotary_dim or None, v_first=v_first,
                                        v_lambda=self.v_lambda if self.value_mix == "mixed" else None,
                                        v_keep=self.value_mix == "first")
+            self._gate(o, qkv, gate_col0)
             ops.scope("attention.o_projection")
             linear(o, self.w_o, residual, self.b_o, accumulate=True)
             return
@@ -214,8 +236,17 @@ class GQAttention(Mixer):
         else:
             ops.attention(q, o, cache.k, cache.v, step, table, self.window or 0, self.scale,
                           self.nq, self.nkv, self.d, workspace=ws, decode_chunk=self.decode_chunk, dv=self.dv, sink=self.sink)
+        self._gate(o, qkv, gate_col0)
         ops.scope("attention.o_projection")
         linear(o, self.w_o, residual, self.b_o, accumulate=True)
+
+    def _gate(self, o: torch.Tensor, qkv: torch.Tensor, gate_col0: int) -> None:
+        """The gate a head and the mixer's constant, on what the output projection reads."""
+        if self.output_gate:
+            ops.scope("attention.output_gate")
+            ops.head_gate(o, qkv[:, gate_col0:], self.nq, self.out_scale)
+        elif self.out_scale != 1.0:
+            raise ops.KernelError("attention: a constant on the output needs the gate's kernel (output_gate)")
 
 
 registry.register("mixer", "gqa_attention", GQAttention)

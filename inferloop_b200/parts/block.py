@@ -6,7 +6,11 @@ Pre-norm (`pre_norm`): h += mixer(norm1(h)); h += ffn(norm2(h))
 Norm on the sublayer's output (`output_norm`): h += norm1(mixer(h)); h += norm2(ffn(h)); and, when the
 layer has one, a third sublayer fed by the token itself: h += norm3(extra(h, token)).  The sublayers read
 the stream as it is (in the compute dtype); each adds into a zeroed 32-bit buffer, and one kernel norms
-that buffer, adds it to the stream, hands the next sublayer its input and zeroes the buffer again."""
+that buffer, adds it to the stream, hands the next sublayer its input and zeroes the buffer again.
+
+Norms on both sides (`sandwich`): h += m * norm1b(mixer(norm1(h))); h += m * norm2b(ffn(norm2(h))) with a constant
+multiplier m on what joins the stream.  The norms are element-wise (Dynamic Tanh), so the norm on a sublayer's
+output, the sum into the stream and the norm in front of the next sublayer are one launch."""
 from __future__ import annotations
 
 from typing import List, Mapping
@@ -17,7 +21,7 @@ from ..csrc import ops
 from ..weights.decl import WeightDecl
 from . import registry
 from .base import Block, CacheNeeds
-from .norm import RMSNorm
+from .norm import DynamicTanh, RMSNorm
 
 
 class PreNormBlock(Block):
@@ -160,5 +164,75 @@ class OutputNormBlock(Block):
             memo[self.PREPARED] = prepared
 
 
+class SandwichBlock(Block):
+    """spec: hidden_size; residual_mult (default 1); tensor-name pieces mixer_prefix, ffn_prefix, mixer_norm, mixer_out_norm,
+    ffn_norm, ffn_out_norm (under the layer prefix).  The layer's norm must be of kind `dyt`."""
+
+    ZEROED = "sandwich.zeroed"       # memo key: the sublayers' 32-bit buffer that the block before left at zero
+
+    def __init__(self, spec, ctx, prefix: str = "", layer=None) -> None:
+        super().__init__(spec, ctx, prefix)
+        self.hidden = int(spec["hidden_size"])
+        self.mult = float(spec.get("residual_mult", 1.0))
+        make = lambda key, default: registry.build_norm(layer.norm, ctx, prefix + spec.get(key, default), width=self.hidden)
+        self.norm1, self.norm1b = make("mixer_norm", "norm1"), make("mixer_out_norm", "norm1b")
+        self.norm2, self.norm2b = make("ffn_norm", "norm2"), make("ffn_out_norm", "norm2b")
+        self.mixer = registry.build("mixer", layer.mixer, ctx, prefix + spec.get("mixer_prefix", "mix."))
+        self.ffn = registry.build("feed_forward", layer.feed_forward, ctx, prefix + spec.get("ffn_prefix", "mlp."))
+        self.has_ffn = not getattr(self.ffn, "absent", False)
+        for n in (self.norm1, self.norm1b, self.norm2, self.norm2b):
+            if not isinstance(n, DynamicTanh):
+                raise ValueError("sandwich: the norms around a sublayer must be element-wise (kind 'dyt')")
+
+    PREPARED = ZEROED
+
+    @property
+    def graph_safe(self) -> bool:
+        return bool(self.mixer.graph_safe and (not self.has_ffn or self.ffn.graph_safe))
+
+    def declare_weights(self) -> List[WeightDecl]:
+        second = self.norm2.declare_weights() + self.norm2b.declare_weights()
+        if not self.has_ffn:          # the absent sublayer's norms may be stored; they are not read
+            second = [WeightDecl(d.name, d.shape, d.role, d.init, d.root, True) for d in second]
+        return (self.norm1.declare_weights() + self.norm1b.declare_weights() + self.mixer.declare_weights() + second
+                + self.ffn.declare_weights())
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        for part in (self.norm1, self.norm1b, self.mixer) + ((self.norm2, self.norm2b, self.ffn) if self.has_ffn else ()):
+            part.bind(tensors)
+
+    def cache_needs(self) -> CacheNeeds:
+        return self.mixer.cache_needs()
+
+    def scratch_bytes(self, tokens: int) -> int:
+        size = torch.empty((), dtype=self.ctx.dtype).element_size()
+        return tokens * self.hidden * (size + 4) + max(self.mixer.scratch_bytes(tokens), self.ffn.scratch_bytes(tokens) if self.has_ffn else 0)
+
+    def forward(self, hidden: torch.Tensor, step, cache) -> None:
+        ws = self.ctx.workspace
+        x = ws.buffer("block.normed", hidden.shape, self.ctx.dtype)          # what a sublayer reads
+        y = ws.buffer("block.sublayer_out", hidden.shape, torch.float32)     # what it adds into
+        memo = getattr(step, "memo", None)
+        zeroed = (y.data_ptr(), tuple(hidden.shape))
+        ops.scope("norm")
+        if memo is None or memo.pop(self.ZEROED, None) != zeroed:
+            ops.cast_zero(hidden, x, y)
+        self.norm1.forward(hidden, x)
+        ops.scope("mixer")
+        self.mixer.forward(x, y, step, cache)
+        ops.scope("norm")
+        if self.has_ffn:
+            ops.dyt_add(y, self.norm1b.tensors, self.mult, hidden, next_norm=self.norm2.tensors, out=x, zero=True)
+            ops.scope("feed_forward")
+            self.ffn.forward(x, y, step)
+            ops.scope("norm")
+            ops.dyt_add(y, self.norm2b.tensors, self.mult, hidden, zero=True)
+        else:
+            ops.dyt_add(y, self.norm1b.tensors, self.mult, hidden, zero=True)
+        if memo is not None:
+            memo[self.ZEROED] = zeroed
+
+
 registry.register("block", "pre_norm", PreNormBlock)
+registry.register("block", "sandwich", SandwichBlock)
 registry.register("block", "output_norm", OutputNormBlock)

@@ -9,6 +9,9 @@ followed, when the spec names a norm, by that norm (an RMS norm: fused into the 
 token before a step's first token is state of the request: one int32 per state slot, written after
 every step.  With `keep`, the rows are also left in the workspace buffer of that name, [tokens,
 hidden] 32-bit, for blocks that read the embedding's output later.  `buckets` 0: no second table.
+
+`normed`: the token's row of the token table (times `scale`, default 1), then the norm the spec names (any norm
+that can write over its own input: an element-wise one).
 """
 from __future__ import annotations
 
@@ -71,4 +74,28 @@ class HashedPairsEmbedding(Embedding):
             ops.store_last_tokens(step, prev)
 
 
+class NormedEmbedding(Embedding):
+    graph_safe = True
+    """spec: hidden_size, norm (a PartSpec of role norm), norm_name (the norm's tensor prefix), scale (default 1)."""
+
+    def __init__(self, spec, ctx, prefix: str = "") -> None:
+        super().__init__(spec, ctx, prefix)
+        self.hidden = int(spec["hidden_size"])
+        self.scale = float(spec.get("scale", 1.0))
+        self.norm = registry.build_norm(spec["norm"], ctx, prefix + str(spec.get("norm_name", "embed_norm.")), width=self.hidden)
+        if not getattr(self.norm, "graph_safe", False):
+            raise ValueError("normed embedding: the norm must read the batch from device memory alone")
+
+    def declare_weights(self) -> List[WeightDecl]:
+        return self.norm.declare_weights()
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.norm.bind(tensors)
+
+    def forward(self, step, table: torch.Tensor, hidden: torch.Tensor, state: Mapping[str, torch.Tensor]) -> None:
+        ops.embed(step.tokens, table, hidden, self.scale, 1)
+        self.norm.forward(hidden, hidden)
+
+
 registry.register("embedding", "hashed_pairs", HashedPairsEmbedding)
+registry.register("embedding", "normed", NormedEmbedding)

@@ -16,6 +16,7 @@ from typing import List, Mapping
 
 import torch
 
+from ..config.spec import PartSpec
 from ..csrc import ops
 from ..weights.decl import WeightDecl
 from .base import FeedForward
@@ -35,8 +36,18 @@ class SwiGLU(FeedForward):
                 raise ValueError(f"swiglu has no tensor role {role!r}")
             names[role] = name
         self.names = {k: prefix + v for k, v in names.items()}
-        # what the gate passes through: "silu" (SwiGLU) or "relu"
-        self.activation = str(spec.get("activation", "silu"))
+        # what the gate passes through: "silu" (SwiGLU) or "relu"; or a PartSpec of kind "clamped_glu" (limit, sharpness,
+        # up_offset): a(min(gate, limit)) * (clamp(up, -limit, limit) + up_offset) with a(g) = g * sigmoid(sharpness * g)
+        act = spec.get("activation", "silu")
+        self.glu = None
+        if isinstance(act, PartSpec):
+            if act.kind != "clamped_glu":
+                raise ValueError(f"gated feed-forward: unknown activation {act.kind!r}")
+            self.glu = (float(act["limit"]), float(act.get("sharpness", 1.0)), float(act.get("up_offset", 0.0)))
+            if self.glu[0] <= 0:
+                raise ValueError("clamped_glu: limit must be positive")
+            act = "silu"
+        self.activation = str(act)
         if self.activation not in ops.GATE_ACTIVATIONS:
             raise ValueError(f"gated feed-forward: unknown activation {self.activation!r}")
         self.w_gate_up = self.w_down = None
@@ -51,7 +62,7 @@ class SwiGLU(FeedForward):
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         n = self.names
         gate, up = tensors[n["gate"]], tensors[n["up"]]
-        self.fused = gate.dtype == torch.bfloat16 and self.inter % 64 == 0 and self.hidden % 8 == 0
+        self.fused = self._fusable(gate.dtype)
         if self.fused:
             blocks = self.inter // 64
             self.w_gate_up = torch.stack(
@@ -61,9 +72,13 @@ class SwiGLU(FeedForward):
             self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = tensors[n["down"]].contiguous()
 
+    def _fusable(self, dtype: torch.dtype) -> bool:
+        """Whether the gated unit is taken in the tensor-core product's epilogue (gate and up rows interleaved)."""
+        return dtype == torch.bfloat16 and self.inter % 64 == 0 and self.hidden % 8 == 0 and self.glu is None
+
     def scratch_bytes(self, tokens: int) -> int:
         size = torch.empty((), dtype=self.ctx.dtype).element_size()
-        fused = self.ctx.dtype == torch.bfloat16 and self.inter % 64 == 0 and self.hidden % 8 == 0
+        fused = self._fusable(self.ctx.dtype)
         return tokens * self.inter * size * (1 if fused else 3)
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor, step, accumulate: bool = True) -> None:
@@ -73,14 +88,17 @@ class SwiGLU(FeedForward):
         act = ws.buffer("mlp.act", (T, self.inter), dt)
         ops.scope("feed_forward.gate_up (gate inside)" if self.fused else "feed_forward.gate_up")
         if self.fused and ops.gemm_tc_eligible(x, self.w_gate_up, act):
-            ops.gemm_tc(x, self.w_gate_up, act, swiglu=True, gate=self.activation)
+            ops.gemm_tc(x, self.w_gate_up, act, swiglu=True, gate=self.activation, glu=self.glu)
         elif self.fused:
             raise ops.KernelError("SwiGLU: the interleaved weight needs the tensor-core GEMM, which refused this input")
         else:
             gate_up = ws.buffer("mlp.gate_up", (T, 2 * self.inter), dt)
             linear(x, self.w_gate_up, gate_up)
             ops.scope("feed_forward.swiglu")
-            ops.silu_mul(gate_up, act, self.activation)
+            if self.glu is not None:
+                ops.glu_mul(gate_up, act, *self.glu)
+            else:
+                ops.silu_mul(gate_up, act, self.activation)
         ops.scope("feed_forward.down")
         linear(act, self.w_down, residual, accumulate=accumulate)
 

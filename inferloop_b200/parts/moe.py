@@ -8,6 +8,9 @@
   y = sum_j expert_j(w_j x)     (`weight_on` = "input")   or   sum_j w_j expert_j(x)   ("output")
   y += sigmoid(W_gate x) * shared(x)    when the description has a shared expert (`shared_inter`;
   `shared_gate` False leaves the multiplier out)
+  (`correction`: the experts are ranked by s + c with a stored vector c, the weights stay s;  `groups` = (count, keep):
+  the experts form `count` equal groups of neighbours, a group ranks by its best member, and only experts of the best
+  `keep` groups can be chosen;  `renorm_eps` joins the sum that `renormalize` divides by;  `route_scale` multiplies the weights)
 
 The experts' matrices are stacked at load into [experts, 2 I, H] (gate rows, then up rows) and
 [experts, H, I].  A step sorts its (token, choice) pairs by expert on the device into rows
@@ -48,6 +51,15 @@ class RoutedExperts(FeedForward):
         self.renormalize = bool(spec.get("renormalize", False))
         self.weight_on = str(spec.get("weight_on", "output"))
         self.router_bias = bool(spec.get("router_bias", False))       # a vector added to the router's logits
+        self.correction = bool(spec.get("correction", False))         # a vector added to the scores for the ranking alone
+        groups = spec.get("groups")
+        self.groups, self.keep = (int(groups[0]), int(groups[1])) if groups else (1, 1)
+        self.route_scale = float(spec.get("route_scale", 1.0))
+        self.renorm_eps = float(spec.get("renorm_eps", 0.0))
+        if self.groups < 1 or self.experts % self.groups or not 1 <= self.keep <= self.groups or self.groups > 32:
+            raise ValueError(f"routed feed-forward: {self.groups} groups (keeping {self.keep}) of {self.experts} experts")
+        if self.top > self.experts // self.groups * self.keep:
+            raise ValueError(f"routed feed-forward: top {self.top} exceeds the experts of the {self.keep} kept groups")
         # the experts' gated unit: a(gate) * (up + up_offset), a(g) = g * sigmoid(sharpness * g); kind "clamped_glu" also
         # takes min(gate, limit) and clamp(up, -limit, limit) first.  (limit, sharpness, up_offset); the default is SwiGLU.
         act = spec.get("activation")
@@ -68,7 +80,7 @@ class RoutedExperts(FeedForward):
         if not 0 < self.top <= self.experts:
             raise ValueError(f"top_k {self.top} of {self.experts} experts")
         # tensor names under the prefix: {e} is the expert's number
-        names = {"router": "router.weight", "router_bias": "router.bias", "gate": "experts.{e}.gate_proj.weight", "up": "experts.{e}.up_proj.weight",
+        names = {"router": "router.weight", "router_bias": "router.bias", "correction": "router.correction", "gate": "experts.{e}.gate_proj.weight", "up": "experts.{e}.up_proj.weight",
                  "down": "experts.{e}.down_proj.weight", "shared_gate": "shared_expert_gate.weight",
                  "shared_prefix": "shared_expert."}
         for role, name in spec.get("names", ()):
@@ -80,7 +92,7 @@ class RoutedExperts(FeedForward):
         if self.shared_inter:
             self.shared = SwiGLU(PartSpec.make("swiglu", hidden_size=self.hidden, intermediate_size=self.shared_inter,
                                                names=tuple(spec.get("shared_names", ()))), ctx, self.names["shared_prefix"])
-        self.w_router = self.w_gate_up = self.w_down = self.b_router = None
+        self.w_router = self.w_gate_up = self.w_down = self.b_router = self.c_router = None
         self.fused = False          # gate/up rows interleaved for the tensor-core product's SwiGLU epilogue
 
     # ------------------------------------------------------------------ weights
@@ -89,6 +101,8 @@ class RoutedExperts(FeedForward):
         out = [WeightDecl(n["router"], (self.experts, H))]
         if self.router_bias:
             out.append(WeightDecl(n["router_bias"], (self.experts,), "vector", "bias"))
+        if self.correction:
+            out.append(WeightDecl(n["correction"], (self.experts,), "vector", "bias"))
         for e in range(self.experts):
             out += [WeightDecl(n["gate"].format(e=e), (I, H)), WeightDecl(n["up"].format(e=e), (I, H)),
                     WeightDecl(n["down"].format(e=e), (H, I))]
@@ -104,6 +118,8 @@ class RoutedExperts(FeedForward):
         self.w_router = torch.cat(rows, dim=0).contiguous()
         if self.router_bias:
             self.b_router = tensors[n["router_bias"]].contiguous()
+        if self.correction:
+            self.c_router = tensors[n["correction"]].contiguous()
         gates = [tensors[n["gate"].format(e=e)] for e in range(self.experts)]
         ups = [tensors[n["up"].format(e=e)] for e in range(self.experts)]
         self.fused = gates[0].dtype == torch.bfloat16 and self.inter % 64 == 0 and self.hidden % 8 == 0
@@ -149,7 +165,8 @@ class RoutedExperts(FeedForward):
         ops.moe_logits(x, self.w_router, logits)
         choice = ws.buffer("moe.choice", (T * K,), torch.int32)
         weight = ws.buffer("moe.weight", (T * K,), torch.float32)
-        ops.moe_route(logits, E, K, self.score == "softmax", self.renormalize, choice, weight, bias=self.b_router)
+        ops.moe_route(logits, E, K, self.score == "softmax", self.renormalize, choice, weight, bias=self.b_router,
+                      correction=self.c_router, groups=self.groups, keep=self.keep, scale=self.route_scale, renorm_eps=self.renorm_eps)
         pos = ws.buffer("moe.pos", (T * K,), torch.int32)
         block_expert = ws.buffer("moe.block_expert", (rows // block,), torch.int32)
         ops.moe_plan(choice, E, block, pos, block_expert)

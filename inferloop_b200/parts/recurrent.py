@@ -1,0 +1,222 @@
+"""Mixers with a state of fixed size per request, and the mixer that runs several mixers side by side.
+
+`gated_linear_recurrence` (the recurrent block of Griffin with its real-gated linear recurrent unit):
+
+    y = gelu_tanh(W_y h + b_y);  u = causal conv over `taps` tokens, per channel, with bias, of (W_x h + b_x)
+    u is cut into `blocks` equal parts; in part b: r = sigmoid(Ra_b u_b + ra_b), i = sigmoid(Ri_b u_b + ri_b)
+    a = exp(-rate * r * softplus(lam));   S_t = a S_{t-1} + sqrt(1 - a^2) * i * u_t;   out = W_o (S * y)
+
+State per request: S [width] in 32-bit and the last taps - 1 inputs of the convolution.  The two input
+products are one product; the convolution is the state-space layer's (without its activation); the gates'
+block-diagonal products run in 32-bit (per-block product of csrc/latent.cu on 32-bit lanes); the gates, the
+decay, the recurrence and the output gate are one kernel (csrc/recurrent.cu), chunked for long portions.
+
+`decayed_linear_attention` (lightning attention): q, k, v = silu(W h) per head, S_t = decay_h S_{t-1} + k_t v_t^T,
+o_t = S_t^T q_t; the heads together are RMS-normed with a weight, multiplied by sigmoid(W_g h) and by the
+constant `out_scale`, and projected.  State per request: S [heads, dim, vdim] in 32-bit.  The recurrence is the
+state-space layer's scan with a stored decay and unit step sizes (csrc/ssm.cu, `fixed`), so long portions run in
+chunks side by side.
+
+`parallel`: several mixers read the same input and add into the same output, each with its own tensors under its
+own prefix, its own cache (at most one of them paged) and its own constant on its output.
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import List, Mapping
+
+import torch
+
+from ..csrc import ops
+from ..weights.decl import WeightDecl
+from . import registry
+from .base import CacheNeeds, Mixer, SlotStateNeed
+from .linear import linear
+
+
+def _names(defaults: dict, spec, prefix: str, what: str) -> dict:
+    names = dict(defaults)
+    for role, name in spec.get("names", ()):
+        if role not in names:
+            raise ValueError(f"{what} has no tensor role {role!r}")
+        names[role] = name
+    return {k: prefix + v for k, v in names.items()}
+
+
+class GatedLinearRecurrence(Mixer):
+    graph_safe = True
+
+    def __init__(self, spec, ctx, prefix: str = "") -> None:
+        super().__init__(spec, ctx, prefix)
+        self.hidden = int(spec["hidden_size"])
+        self.width = int(spec["width"])
+        self.blocks = int(spec["blocks"])
+        self.taps = int(spec["taps"])
+        self.rate = float(spec.get("rate", 8.0))
+        self.out_scale = float(spec.get("out_scale", 1.0))
+        if self.out_scale != 1.0:
+            raise ValueError("gated_linear_recurrence: no constant on the output is served")
+        if self.blocks < 1 or self.width % self.blocks:
+            raise ValueError(f"{self.width} channels cannot be cut into {self.blocks} equal blocks")
+        self.block_width = self.width // self.blocks
+        self.names = _names({"y": "y", "yb": "y.b", "x": "x", "xb": "x.b", "conv": "conv", "conv_bias": "conv.b", "ra": "ra",
+                             "rab": "ra.b", "ri": "ri", "rib": "ri.b", "lam": "lam", "o": "o"}, spec, prefix, "the gated recurrence")
+        self.w_in = self.b_in = self.conv_w = self.conv_b = self.w_gates = self.r_bias = self.i_bias = self.lam = self.w_o = None
+
+    def declare_weights(self) -> List[WeightDecl]:
+        n, W, H, B, bw = self.names, self.width, self.hidden, self.blocks, self.block_width
+        return [WeightDecl(n["y"], (W, H)), WeightDecl(n["yb"], (W,), "vector", "bias"),
+                WeightDecl(n["x"], (W, H)), WeightDecl(n["xb"], (W,), "vector", "bias"),
+                WeightDecl(n["conv"], (W, self.taps), "vector", "mix"), WeightDecl(n["conv_bias"], (W,), "vector", "bias"),
+                WeightDecl(n["ra"], (B, bw, bw)), WeightDecl(n["rab"], (B, bw), "vector", "bias"),
+                WeightDecl(n["ri"], (B, bw, bw)), WeightDecl(n["rib"], (B, bw), "vector", "bias"),
+                WeightDecl(n["lam"], (W,), "vector", "around_zero"), WeightDecl(n["o"], (H, W))]
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        n = self.names
+        self.w_in = torch.cat([tensors[n["y"]], tensors[n["x"]]], dim=0).contiguous()          # one product gives y | x
+        self.b_in = torch.cat([tensors[n["yb"]], tensors[n["xb"]]]).contiguous()
+        self.conv_w = tensors[n["conv"]].contiguous()
+        self.conv_b = tensors[n["conv_bias"]].contiguous()
+        # a block's two gate matrices side by side, [blocks, in, 2 out], in 32-bit: the gates are 32-bit arithmetic
+        ra, ri = tensors[n["ra"]].float(), tensors[n["ri"]].float()
+        self.w_gates = torch.cat([ra.transpose(1, 2), ri.transpose(1, 2)], dim=2).contiguous()
+        self.r_bias = tensors[n["rab"]].reshape(-1).contiguous()
+        self.i_bias = tensors[n["rib"]].reshape(-1).contiguous()
+        self.lam = tensors[n["lam"]].contiguous()
+        self.w_o = tensors[n["o"]].contiguous()
+
+    def cache_needs(self) -> CacheNeeds:
+        return CacheNeeds(slots=(SlotStateNeed("state", (self.width,), torch.float32),
+                                 SlotStateNeed("conv", (max(self.taps - 1, 0), self.width), torch.float32)))
+
+    def scratch_bytes(self, tokens: int) -> int:
+        size = torch.empty((), dtype=self.ctx.dtype).element_size()
+        chunks = -(-tokens // ops.LRU_CHUNK) + 1
+        return tokens * self.width * (3 * size + 3 * 4) + 2 * chunks * self.width * 4
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, step, cache) -> None:
+        T, W, ws, dt = x.shape[0], self.width, self.ctx.workspace, self.ctx.dtype
+        proj = ws.buffer("lru.proj", (T, 2 * W), dt)
+        ops.scope("recurrence.in_projection")
+        linear(x, self.w_in, proj, self.b_in)
+        ops.scope("recurrence.convolution")
+        u = ws.buffer("lru.u", (T, W), torch.float32)
+        ops.ssm_conv(proj, W, W, self.conv_w, self.conv_b, cache.state["conv"], step, u, activation="none")
+        ops.scope("recurrence.gates")
+        gates = ws.buffer("lru.gates", (T, 2 * W), torch.float32)
+        ops.head_matmul(u, self.w_gates, gates)
+        ops.scope("recurrence.scan")
+        gated = ws.buffer("lru.gated", (T, W), dt)
+        ops.lru_scan(gates, u, proj, 0, self.r_bias, self.i_bias, self.lam, self.rate, cache.state["state"], gated, step,
+                     self.block_width, workspace=ws)
+        ops.scope("recurrence.out_projection")
+        linear(gated, self.w_o, residual, accumulate=True)
+
+
+class DecayedLinearAttention(Mixer):
+    graph_safe = True
+
+    def __init__(self, spec, ctx, prefix: str = "") -> None:
+        super().__init__(spec, ctx, prefix)
+        self.hidden = int(spec["hidden_size"])
+        self.heads = int(spec["heads"])
+        self.d = int(spec["head_dim"])
+        self.dv = int(spec["v_head_dim"])
+        self.decay = tuple(float(v) for v in spec["decay"])
+        self.eps = float(spec["eps"])
+        self.out_scale = float(spec.get("out_scale", 1.0))
+        if len(self.decay) != self.heads or any(not 0.0 <= v <= 1.0 for v in self.decay):
+            raise ValueError(f"decayed_linear_attention: {self.heads} heads need as many decays in [0, 1], found {self.decay}")
+        self.inner = self.heads * self.dv
+        self.channels = self.inner + 2 * self.heads * self.d           # v | k | q: what the recurrence reads
+        self.names = _names({"q": "q", "k": "k", "v": "v", "g": "g", "norm": "norm", "o": "o"}, spec, prefix, "the linear attention")
+        self.w_in = self.norm_w = self.w_o = self.decays = None
+
+    def declare_weights(self) -> List[WeightDecl]:
+        n, H = self.names, self.hidden
+        return [WeightDecl(n["q"], (self.heads * self.d, H)), WeightDecl(n["k"], (self.heads * self.d, H)),
+                WeightDecl(n["v"], (self.inner, H)), WeightDecl(n["g"], (self.inner, H)),
+                WeightDecl(n["norm"], (self.inner,), "vector", "norm"), WeightDecl(n["o"], (H, self.inner))]
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        n = self.names
+        # one product gives v | k | q | g: the recurrence reads values, keys and queries in that order
+        self.w_in = torch.cat([tensors[n["v"]], tensors[n["k"]], tensors[n["q"]], tensors[n["g"]]], dim=0).contiguous()
+        self.norm_w = tensors[n["norm"]].contiguous()
+        self.w_o = tensors[n["o"]].contiguous()
+        self.decays = torch.tensor(self.decay, dtype=torch.float32, device=self.w_o.device)
+
+    def cache_needs(self) -> CacheNeeds:
+        return CacheNeeds(slots=(SlotStateNeed("state", (self.heads, self.d, self.dv), torch.float32),))
+
+    def scratch_bytes(self, tokens: int) -> int:
+        size = torch.empty((), dtype=self.ctx.dtype).element_size()
+        chunks = -(-tokens // ops.SSM_CHUNK) + 1
+        return (tokens * ((self.channels + 2 * self.inner) * size + (self.channels + self.inner) * 4)
+                + chunks * self.heads * (self.d * self.dv + 1) * 4)
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, step, cache) -> None:
+        T, ws, dt = x.shape[0], self.ctx.workspace, self.ctx.dtype
+        proj = ws.buffer("linattn.proj", (T, self.channels + self.inner), dt)
+        ops.scope("linear_attention.in_projection")
+        linear(x, self.w_in, proj)
+        ops.scope("linear_attention.activation")
+        act = ws.buffer("linattn.act", (T, self.channels), torch.float32)
+        ops.silu_rows(proj, self.channels, act)
+        ops.scope("linear_attention.scan")
+        y = ws.buffer("linattn.y", (T, self.inner), torch.float32)
+        ops.ssm_scan(act, None, 0, None, self.decays, None, cache.state["state"], y, step, self.heads, self.dv, self.d, self.heads,
+                     workspace=ws, fixed_decay=True)
+        ops.scope("linear_attention.norm_gate")
+        gated = ws.buffer("linattn.gated", (T, self.inner), dt)
+        ops.rms_gate(y, proj[:, self.channels:], self.norm_w, self.eps, gated, self.out_scale)
+        ops.scope("linear_attention.out_projection")
+        linear(gated, self.w_o, residual, accumulate=True)
+
+
+class ParallelMixers(Mixer):
+    """spec: `branches` = ((sub-prefix, PartSpec of role mixer), ...).  Every branch reads the block's input and adds
+    into the block's output; a branch's constant on its output is its own parameter (`out_scale`)."""
+
+    def __init__(self, spec, ctx, prefix: str = "") -> None:
+        super().__init__(spec, ctx, prefix)
+        branches = tuple(spec["branches"])
+        if not branches:
+            raise ValueError("parallel: no branches")
+        self.parts = [registry.build("mixer", part, ctx, prefix + sub) for sub, part in branches]
+        if sum(1 for p in self.parts if p.cache_needs().paged is not None) > 1:
+            raise ValueError("parallel: at most one branch may keep keys and values in pages")
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(p.graph_safe for p in self.parts)
+
+    def declare_weights(self) -> List[WeightDecl]:
+        return [d for p in self.parts for d in p.declare_weights()]
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        for p in self.parts:
+            p.bind(tensors)
+
+    def cache_needs(self) -> CacheNeeds:
+        paged, slots = None, []
+        for i, p in enumerate(self.parts):
+            need = p.cache_needs()
+            paged = need.paged if need.paged is not None else paged
+            slots += [SlotStateNeed(f"{i}.{s.name}", s.shape, s.dtype) for s in need.slots]
+        return CacheNeeds(paged=paged, slots=tuple(slots))
+
+    def scratch_bytes(self, tokens: int) -> int:
+        return sum(p.scratch_bytes(tokens) for p in self.parts)
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, step, cache) -> None:
+        for i, p in enumerate(self.parts):
+            tag = f"{i}."
+            own = dataclasses.replace(cache, state={k[len(tag):]: v for k, v in cache.state.items() if k.startswith(tag)})
+            p.forward(x, residual, step, own)
+
+
+registry.register("mixer", "gated_linear_recurrence", GatedLinearRecurrence)
+registry.register("mixer", "decayed_linear_attention", DecayedLinearAttention)
+registry.register("mixer", "parallel", ParallelMixers)

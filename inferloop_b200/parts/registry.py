@@ -65,4 +65,4 @@ def _ensure_builtin() -> None:
     if _BUILTIN_DONE:
         return
     _BUILTIN_DONE = True
-    from . import attention, block, embedding, hyper, latent_attention, logits, loop, mlp, moe, norm, rope, side, ssm  # noqa: F401  (they register themselves)
+    from . import attention, block, embedding, hyper, latent_attention, logits, loop, mlp, moe, norm, recurrent, rope, side, ssm  # noqa: F401  (they register themselves)
