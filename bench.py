@@ -223,8 +223,36 @@ def dalavik_numbers(cfg: dict):
     return {"layer_params": params / L, "head_params": V * W, "kv_bytes_per_token": kv, "attn_flops_per_pair": attn, "layers": L}
 
 
+def zebivik_numbers(cfg: dict):
+    """The same for a Zebivik configuration: a parallel layer counts both of its mixers (only the softmax side has keys
+    and values in pages; the linear side and the recurrent layers keep a state per sequence, read and written by a decode
+    step); a routed layer counts the experts one token runs and its shared expert."""
+    W, V, L = cfg["width"], cfg["vocab"], len(cfg["layers"])
+    params, kv, attn, state = 0, 0, 0, 0
+    for layer in cfg["layers"]:
+        m, f = layer["mixer"], layer["mlp"]
+        if layer["type"] == "parallel":
+            a, b = m["left"], m["right"]
+            params += ((a["heads"] + a["kv_heads"]) * a["dim"] + a["kv_heads"] * a["vdim"] + a["heads"] + a["heads"] * a["vdim"]) * W
+            params += (2 * b["heads"] * b["dim"] + 3 * b["heads"] * b["vdim"]) * W
+            kv += a["kv_heads"] * (a["dim"] + a["vdim"]) * 2
+            attn += 2 * a["heads"] * (a["dim"] + a["vdim"])
+            state += 2 * 4 * b["heads"] * b["dim"] * b["vdim"]
+        else:
+            params += 3 * m["width"] * W + 2 * m["width"] * (m["width"] // m["blocks"])
+            state += 2 * 4 * m["width"] * m["conv"]
+        if f is not None and f["kind"] == "dense":
+            params += 3 * W * f["ff"]
+        elif f is not None:
+            params += 3 * W * (f["router"]["top"] * f["expert"]["ff"] + (f.get("shared") or {}).get("ff", 0)) + W * f["router"]["experts"]
+    return {"layer_params": params / L, "head_params": V * W, "kv_bytes_per_token": kv, "attn_flops_per_pair": attn, "layers": L,
+            "state_bytes_per_seq": state}
+
+
 def model_numbers(cfg: dict):
     """Parameters the matrix products of one token touch, and bytes of cache per token."""
+    if cfg.get("architecture") == "Zebivik":
+        return zebivik_numbers(cfg)
     if cfg.get("architecture") == "Dalavik":
         return dalavik_numbers(cfg)
     if cfg.get("architecture") == "Sufolix":
@@ -902,6 +930,71 @@ def run_dalavik(args) -> dict:
     return out
 
 
+# ----------------------------------------------------------------------------- the Zebivik decoder beside Mamevik and Sufolix
+def zebivik_config(kind: str, layers: int, width: int, vocab: int, experts: int, top: int, expert_ff: int) -> dict:
+    """`kind`: "parallel" (every layer is softmax attention with a gate a head beside a linear attention with constant
+    decays), "rglru" (every layer is a gated linear recurrence behind a short convolution) or "mixed" (two recurrent
+    layers, one parallel layer, in turn; the first layer's feed-forward is the clamped dense unit)."""
+    par = {"type": "parallel", "mixer": {
+        "left": {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                 "rot": {"base": 500000.0, "dims": 128, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}},
+        "right": {"heads": 8, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** -(2 + i) for i in range(8)]},
+        "left_scale": 1.0, "right_scale": 0.5}}
+    rec = {"type": "rglru", "mixer": {"width": width, "blocks": width // 256, "conv": 4}}
+    mlp = {"kind": "moe", "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": 4, "keep": 2}}, "expert": {"ff": expert_ff}}
+    pick = {"parallel": lambda i: par, "rglru": lambda i: rec, "mixed": lambda i: par if i % 3 == 2 else rec}[kind]
+    out = [dict(pick(i), mlp=json.loads(json.dumps(mlp))) for i in range(layers)]
+    if kind == "mixed":
+        out[0]["mlp"] = {"kind": "dense", "ff": top * expert_ff, "limit": 7.0}
+    return {"architecture": "Zebivik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "layers": out, "logit_softcap": 30.0}
+
+
+def run_zebivik(args) -> dict:
+    """Decode and prefill of the Zebivik decoder at layer sizes of a real model (parallel attention layers, gated linear
+    recurrences, both in turn), beside the closest models the engine has at the same width, layers and experts: the Mamevik
+    decoder with state-space recurrences (the recurrent layers' relative) and the Sufolix decoder with routed experts (the
+    attention layers' relative); with the device time of every op class."""
+    import torch
+    L, W, V = args.layers if args.layers != FULL_LAYERS else 8, 2048, 32768
+    E, TOP, EFF = 16, 2, 1408
+    which = ["parallel", "rglru", "mixed"] if args.zebivik == "all" else [args.zebivik]
+    out = {"metric": "zebivik_vs_mamevik_and_sufolix_equal_size", "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic",
+           "steps": args.steps, "warmup": args.warmup, "batch": args.batch, "peaks": peaks(), "cases": {}}
+    arms = {kind: zebivik_config(kind, L, W, V, E, TOP, EFF) for kind in which}
+    arms["mamevik"] = mamevik_config("ssd", L, W, V, E, TOP, EFF)
+    arms["sufolix"] = sufolix_config("moe", L, W, 16, 4, 128, 0, E, TOP, EFF, 0, V, 1)
+    arms["sufolix"].pop("streams")
+    for layer in arms["sufolix"]["layers"]:
+        layer["mlp"].pop("shared")
+    for arm, cfg in arms.items():
+        pages = (args.batch * (PROMPT_LEN + args.steps + args.warmup + 64) + PREFILL_LEN) // PAGE + 64
+        bench = Bench(cfg, SEED, pages, max(args.batch, 8), 8192, PREFILL_LEN)
+        with ClockSampler() as clocks:
+            tps, ms, kernels, ctx = bench.decode_device(args.batch, args.steps, args.warmup, arm, PROMPT_LEN)
+        routed = sum(1 for l in cfg["layers"] if l["mlp"] is not None and l["mlp"]["kind"] == "moe")
+        touched = bench.weight_bytes - routed * 3 * W * EFF * 2 * max(0, E - min(E, args.batch * TOP))
+        step_bytes = touched + args.batch * (ctx * bench.nums["kv_bytes_per_token"] + bench.nums.get("state_bytes_per_seq", 0))
+        r = {"decode_tokens_per_s": round(tps, 1), "decode_ms_per_step": round(ms, 4), "kernels_per_step": kernels,
+             "decode_frac_of_hbm": round(step_bytes / (ms / 1e3) / 1e9 / bench.pk["hbm_gbs"], 4),
+             "weights_gb": round(bench.weight_bytes / 1e9, 3), "clocks": clocks.summary(),
+             "prefill": bench.prefill_timed(PREFILL_LEN, 3, PREFILL_SAMPLES)}
+        if args.breakdown:
+            r["breakdown"] = bench.breakdown(args.batch, PROMPT_LEN, PREFILL_LEN)
+        out["cases"][arm] = r
+        del bench
+        torch.cuda.empty_cache()
+    out["sizes"] = {"layers": L, "width": W, "vocab": V, "experts": E, "top": TOP, "expert_ff": EFF,
+                    "mixers": {kind: sorted({json.dumps(l["mixer"], sort_keys=True) for l in arms[kind]["layers"]}) for kind in which}}
+    for kind in which:
+        c = out["cases"][kind]
+        for other in ("mamevik", "sufolix"):
+            base = out["cases"][other]
+            c[f"decode_ms_per_step_over_{other}"] = round(c["decode_ms_per_step"] / base["decode_ms_per_step"], 4)
+            c[f"prefill_ms_over_{other}"] = round(c["prefill"]["ms"] / base["prefill"]["ms"], 4)
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -922,6 +1015,8 @@ def main() -> int:
                     help="the Mamevik decoder beside a Sufolix model with routed experts of equal size (decode, prefill, op classes with --breakdown)")
     ap.add_argument("--dalavik", nargs="?", const="all", default=None, choices=["all", "latent", "heads", "mixed"],
                     help="the Dalavik decoder beside a Sufolix model with a dense feed-forward of equal size (decode, prefill, op classes with --breakdown)")
+    ap.add_argument("--zebivik", nargs="?", const="all", default=None, choices=["all", "parallel", "rglru", "mixed"],
+                    help="the Zebivik decoder beside a Mamevik and a Sufolix model of equal size (decode, prefill, op classes with --breakdown)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -948,6 +1043,9 @@ def main() -> int:
         return 0
     if args.dalavik:
         print(json.dumps(run_dalavik(args)))
+        return 0
+    if args.zebivik:
+        print(json.dumps(run_zebivik(args)))
         return 0
     result = {"8b": run_8b, "14b-mixed": run_14b_mixed, "32b-long": run_32b_long}[args.config](args)
     print(json.dumps(result))
