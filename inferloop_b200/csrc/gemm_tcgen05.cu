@@ -66,8 +66,16 @@ enum Epilogue : int { kStore = 0, kAccumulate = 1, kSwiGLU = 2 };
 // silu(g) * u with the fast reciprocal: the quotient is within 2 ulp, far inside what the
 // bfloat16 result keeps, and an epilogue thread has 128 of these per tile.
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
-// The gated unit's epilogue: act(gate) * up with act = silu, or relu when `relu` is set.
-__device__ __forceinline__ float gate_mul(int relu, float g, float u) { return relu ? fmaxf(g, 0.f) * u : silu_mul(g, u); }
+// The gated unit's epilogue: act(gate) * up with act = silu (gate_relu 0) or relu (1); or (2) the clamped unit
+// a(min(gate, L)) * (clamp(up, -L, L) + offset) with a(g) = g * sigmoid(sharpness * g).
+template <typename P>
+__device__ __forceinline__ float gate_mul(const P& p, float g, float u) {
+  if (p.gate_relu == 0) return silu_mul(g, u);
+  if (p.gate_relu == 1) return fmaxf(g, 0.f) * u;
+  g = fminf(g, p.act_limit);
+  u = fminf(fmaxf(u, -p.act_limit), p.act_limit);
+  return __fdividef(g, 1.0f + __expf(-p.act_sharp * g)) * (u + p.act_offset);
+}
 
 // K-major operand tile in shared memory, 128-byte swizzle: rows of 128 bytes, 8-row
 // groups 1024 bytes apart.
@@ -97,7 +105,8 @@ struct Params {
   int cluster;               // > 1: a tile's K ranges belong to the CTAs of one cluster, added through their shared memory
   int tma_out;               // many tokens: the result leaves through shared memory and TMA stores (adds, when accumulating)
   int red_out;               // few tokens, accumulating: the K ranges of a tile are separate CTAs whose shares meet in memory (red.add)
-  int gate_relu;             // the gated epilogue's activation: 0 silu, 1 relu
+  int gate_relu;             // the gated epilogue's activation: 0 silu, 1 relu, 2 the clamped unit with the constants below
+  float act_limit, act_sharp, act_offset;
 };
 
 // Work: first `dp_waves` rounds of WHOLE tiles in wave order (round w: CTA c takes tile
@@ -441,7 +450,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           for (int j = 0; j < 4; ++j) {
             const int m = y0 + cg * 4 + j;
             if (m < p.M && n < n_end) {
-              const float val = sw ? gate_mul(p.gate_relu, acc[j], up[j]) : acc[j] + bv + old[j];
+              const float val = sw ? gate_mul(p, acc[j], up[j]) : acc[j] + bv + old[j];
               const size_t o = (size_t)m * p.ldo + n;
               if (p.out_f32) ((float*)p.out)[o] = val; else ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(val);
             }
@@ -598,7 +607,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 fetch(cb + 32 * half, g);
                 fetch(cb + 64 + 32 * half, u);
 #pragma unroll
-                for (int c = 0; c < 32; ++c) r[c] = gate_mul(p.gate_relu, g[c], u[c]);
+                for (int c = 0; c < 32; ++c) r[c] = gate_mul(p, g[c], u[c]);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) piece[4 * half + j] = pack8(r + 8 * j);
               }
@@ -656,7 +665,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                   const int m = y0 + c0 + c;
                   if (m < p.M) {
                     const float g = v[c], u = xch[c * 64 + row];
-                    const float r = gate_mul(p.gate_relu, g, u);
+                    const float r = gate_mul(p, g, u);
                     const size_t o = (size_t)m * p.ldo + i;
                     if (p.out_f32) ((float*)p.out)[o] = r; else ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(r);
                   }
@@ -674,7 +683,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 const int i0 = (y0 + cb) / 2 + (c0 - cb);
                 float r[32];
 #pragma unroll
-                for (int c = 0; c < CH; ++c) r[c] = gate_mul(p.gate_relu, g[c], u[c]);
+                for (int c = 0; c < CH; ++c) r[c] = gate_mul(p, g[c], u[c]);
                 if (xr < p.M) {
                   const size_t o = (size_t)xr * p.ldo + i0;
                   const bool full = i0 + CH <= half_n && (p.ldo % 8 == 0) && ((uintptr_t)p.out % 16 == 0) && !p.out_f32;
@@ -850,7 +859,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           const int c = cb + j * cstep, m = y0 + c;
           if (c < BN && m < p.M && n < n_end) {
             const float g = acc[j];
-            const float v = sw ? gate_mul(p.gate_relu, g, up[j]) : g + bv + old[j];
+            const float v = sw ? gate_mul(p, g, up[j]) : g + bv + old[j];
             const size_t o = (size_t)m * p.ldo + n;
             if (p.out_f32) ((float*)p.out)[o] = v; else ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v);
           }
@@ -898,7 +907,8 @@ struct PairParams {
   int n_whole, rest, split;  // tiles that are one item each; tiles cut into `split` K ranges
   int n_items;               // n_whole + rest * split
   int epilogue, out_f32;
-  int gate_relu;             // the gated epilogue's activation: 0 silu, 1 relu
+  int gate_relu;             // the gated epilogue's activation: 0 silu, 1 relu, 2 the clamped unit with the constants below
+  float act_limit, act_sharp, act_offset;
 };
 
 __global__ void __launch_bounds__(192, 1)
@@ -1075,7 +1085,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             tmem_load_32(taddr + cb + 32 * half, g);
             tmem_load_32(taddr + cb + 64 + 32 * half, u);
 #pragma unroll
-            for (int c = 0; c < 32; ++c) r[c] = gate_mul(p.gate_relu, g[c], u[c]);
+            for (int c = 0; c < 32; ++c) r[c] = gate_mul(p, g[c], u[c]);
 #pragma unroll
             for (int j = 0; j < 4; ++j) piece[4 * half + j] = pack8(r + 8 * j);
           }
@@ -1559,14 +1569,15 @@ int launch_pair(const CUtensorMap& mx, const CUtensorMap& my, const CUtensorMap&
 ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void* out, int out_f32,
                            int M, int N, int K, int lda, int ldw, int ldo, int accumulate /* Epilogue */,
                            float* workspace, long long workspace_floats, int* tickets, int n_tickets,
-                           int* error_flag, int max_ctas, cudaStream_t stream) {
+                           int* error_flag, int max_ctas, float act_limit, float act_sharp, float act_offset, cudaStream_t stream) {
   ILB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
   ILB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
               "gemm_tc: K (%d) and the leading dimensions (%d, %d) must be multiples of 8", K, lda, ldw);
   ILB_REQUIRE(((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
-  // 3 from the caller: the gated epilogue with relu as the gate's activation (else silu)
-  const int gate_relu = accumulate == 3 ? 1 : 0;
+  // 3 from the caller: the gated epilogue with relu as the gate's activation (else silu); 4: the clamped gated unit
+  const int gate_relu = accumulate == 3 ? 1 : (accumulate == 4 ? 2 : 0);
   if (gate_relu) accumulate = kSwiGLU;
+  ILB_REQUIRE(gate_relu != 2 || act_limit > 0.f, "gemm_tc: the clamped unit needs a positive limit");
   ILB_REQUIRE(accumulate >= 0 && accumulate <= 2, "gemm_tc: unknown epilogue %d", accumulate);
   ILB_REQUIRE(accumulate != 1 || out_f32, "gemm_tc: accumulation needs a 32-bit output");
   if (accumulate == 2) {
@@ -1583,7 +1594,7 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
   p.k_blocks = (K + kBlockK - 1) / kBlockK;
   p.epilogue = accumulate;
   p.out_f32 = out_f32;
-  p.gate_relu = gate_relu;
+  p.gate_relu = gate_relu; p.act_limit = act_limit; p.act_sharp = act_sharp; p.act_offset = act_offset;
 
   Plan plan{};
   const int es = out_f32 ? 4 : 2, out_cols = accumulate == 2 ? N / 2 : N;
@@ -1599,6 +1610,7 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
       q.tiles_m = (M + 2 * kTileX - 1) / (2 * kTileX);
       q.k_blocks = p.k_blocks; q.n_whole = pp.n_whole; q.rest = pp.rest; q.split = pp.split; q.n_items = (int)pp.items;
       q.epilogue = accumulate; q.out_f32 = out_f32; q.gate_relu = gate_relu;
+      q.act_limit = act_limit; q.act_sharp = act_sharp; q.act_offset = act_offset;
       CUtensorMap mx, my, mo;
       if (make_map(&mx, A, M, K, lda, kTileX)) return -1;
       if (make_map(&my, W, N, K, ldw, kPairN / 2)) return -1;

@@ -317,6 +317,96 @@ head_matmul_mma_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_
   }
 }
 
+// The same tiles for 32-bit rows times a bfloat16 matrix with a 32-bit result that keeps 32-bit accuracy: every input is
+// cut into three bfloat16 pieces (x = hi + mid + lo exactly, 8 + 8 + 8 significant bits), each piece's products with the
+// bfloat16 matrix are exact in 32 bits, and the three products are accumulated in 32-bit, the smallest piece first.
+__device__ __forceinline__ void split3(float2 v, uint32_t& hi, uint32_t& mid, uint32_t& lo) {
+  const __nv_bfloat16 h0 = __float2bfloat16_rn(v.x), h1 = __float2bfloat16_rn(v.y);
+  const float r0 = v.x - __bfloat162float(h0), r1 = v.y - __bfloat162float(h1);
+  const __nv_bfloat16 m0 = __float2bfloat16_rn(r0), m1 = __float2bfloat16_rn(r1);
+  const __nv_bfloat16 l0 = __float2bfloat16_rn(r0 - __bfloat162float(m0)), l1 = __float2bfloat16_rn(r1 - __bfloat162float(m1));
+  hi = (uint32_t)__bfloat16_as_ushort(h0) | ((uint32_t)__bfloat16_as_ushort(h1) << 16);
+  mid = (uint32_t)__bfloat16_as_ushort(m0) | ((uint32_t)__bfloat16_as_ushort(m1) << 16);
+  lo = (uint32_t)__bfloat16_as_ushort(l0) | ((uint32_t)__bfloat16_as_ushort(l1) << 16);
+}
+
+__global__ void __launch_bounds__(128)
+head_matmul_split_kernel(const float* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ w, float* __restrict__ out, int ldo,
+                         int n_tokens, int K, int N, int xhs, int ohs) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  __shared__ __align__(16) __nv_bfloat16 ws[kMmaTile][kMmaTile + 8];
+  const int t0 = blockIdx.x * kMmaTile, h = blockIdx.y, n0 = blockIdx.z * kMmaTile;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int r0 = t0 + warp * 16 + g, r1 = r0 + 8;
+  const bool live0 = r0 < n_tokens, live1 = r1 < n_tokens;
+  const float* a0 = x + (size_t)(live0 ? r0 : 0) * ldx + (size_t)h * xhs;
+  const float* a1 = x + (size_t)(live1 ? r1 : 0) * ldx + (size_t)h * xhs;
+  const bool warp_live = t0 + warp * 16 < n_tokens;          // (a warp whose 16 rows are all past the end only helps with the copies)
+  float acc[kMmaTile / 8][4];
+#pragma unroll
+  for (int i = 0; i < kMmaTile / 8; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[i][e] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += kMmaTile) {
+    __syncthreads();
+#pragma unroll
+    for (int it = 0; it < kMmaTile * (kMmaTile / 8) / 128; ++it) {
+      const int idx = threadIdx.x + it * 128, r = idx / (kMmaTile / 8), cv = idx % (kMmaTile / 8);
+      const int k = k0 + r, n = n0 + cv * 8;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (k < K && n < N) v = __ldg(reinterpret_cast<const uint4*>(w + ((size_t)h * K + k) * N + n));
+      *reinterpret_cast<uint4*>(&ws[r][cv * 8]) = v;
+    }
+    __syncthreads();
+    if (!warp_live) continue;
+#pragma unroll
+    for (int kb = 0; kb < kMmaTile / 16; ++kb) {
+      const int c = k0 + kb * 16 + 2 * t;
+      if (k0 + kb * 16 >= K) break;
+      const float2 zero = make_float2(0.f, 0.f);
+      uint32_t hi[4], mid[4], lo[4];
+      split3(live0 ? *reinterpret_cast<const float2*>(a0 + c) : zero, hi[0], mid[0], lo[0]);
+      split3(live1 ? *reinterpret_cast<const float2*>(a1 + c) : zero, hi[1], mid[1], lo[1]);
+      split3(live0 ? *reinterpret_cast<const float2*>(a0 + c + 8) : zero, hi[2], mid[2], lo[2]);
+      split3(live1 ? *reinterpret_cast<const float2*>(a1 + c + 8) : zero, hi[3], mid[3], lo[3]);
+#pragma unroll
+      for (int nd = 0; nd < kMmaTile / 16; ++nd) {
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4_trans(smem_u32(&ws[kb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][nd * 16 + (lane >> 4) * 8]), b0, b1, b2, b3);
+        mma_16816(acc[2 * nd], lo, b0, b1);
+        mma_16816(acc[2 * nd + 1], lo, b2, b3);
+        mma_16816(acc[2 * nd], mid, b0, b1);
+        mma_16816(acc[2 * nd + 1], mid, b2, b3);
+        mma_16816(acc[2 * nd], hi, b0, b1);
+        mma_16816(acc[2 * nd + 1], hi, b2, b3);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kMmaTile / 8; ++i) {
+    const int col = n0 + i * 8 + 2 * t;
+    if (col >= N) continue;
+    if (live0) *reinterpret_cast<float2*>(out + (size_t)r0 * ldo + (size_t)h * ohs + col) = make_float2(acc[i][0], acc[i][1]);
+    if (live1) *reinterpret_cast<float2*>(out + (size_t)r1 * ldo + (size_t)h * ohs + col) = make_float2(acc[i][2], acc[i][3]);
+  }
+}
+
+// x: [T, ldx] 32-bit, head i at columns i * xhs ..; w: [heads, K, N] bfloat16; out: [T, ldo] 32-bit, head i at columns
+// i * ohs ...  K a multiple of 16, N of 8; strides and head offsets even; x and out 8-byte aligned, w 16-byte aligned.
+ILB_EXPORT int ilb_head_matmul_split(const float* x, int ldx, const void* w, float* out, int ldo, int n_tokens, int heads, int K, int N,
+                                     int xhs, int ohs, cudaStream_t stream) {
+  ILB_REQUIRE(n_tokens >= 0 && heads > 0 && heads <= 65535 && K > 0 && N > 0, "head_matmul_split: bad sizes");
+  ILB_REQUIRE(xhs >= K && ohs >= N && ldx >= (heads - 1) * xhs + K && ldo >= (heads - 1) * ohs + N, "head_matmul_split: strides too small");
+  ILB_REQUIRE(K % 16 == 0 && N % 8 == 0 && ldx % 2 == 0 && ldo % 2 == 0 && xhs % 2 == 0 && ohs % 2 == 0 && ((uintptr_t)x % 8 == 0) &&
+              ((uintptr_t)out % 8 == 0) && ((uintptr_t)w % 16 == 0), "head_matmul_split: sizes or alignment not served");
+  if (n_tokens == 0) return 0;
+  const dim3 grid((n_tokens + kMmaTile - 1) / kMmaTile, heads, (N + kMmaTile - 1) / kMmaTile);
+  ILB_REQUIRE(grid.z <= 65535, "head_matmul_split: too many columns");
+  ilb::launch(head_matmul_split_kernel, grid, dim3(128), 0, stream, x, ldx, (const __nv_bfloat16*)w, out, ldo, n_tokens, K, N, xhs, ohs);
+  return check_launch("head_matmul_split");
+}
+
 // x: [T, ldx] of `dtype`, head i at columns i * xhs ..; w: [heads, K, N] of `dtype`; out: [T, ldo] of
 // `out_dtype`, head i at columns i * ohs ... (xhs >= K and ohs >= N: a head's row may hold more than the product reads or writes)
 ILB_EXPORT int ilb_head_matmul(const void* x, int dtype, int ldx, const void* w, void* out, int out_dtype, int ldo,

@@ -299,6 +299,22 @@ def head_matmul(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, x_head_stri
           _i(x.shape[0]), _i(heads), _i(K), _i(N), _i(xhs), _i(ohs), _stream(out))
 
 
+def head_matmul_split_supported(K: int, N: int, ldx: int, ldo: int) -> bool:
+    """Sizes that :func:`head_matmul_split` takes."""
+    return K % 16 == 0 and N % 8 == 0 and ldx % 2 == 0 and ldo % 2 == 0
+
+
+def head_matmul_split(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i, :N] = x[t, i, :K] @ w[i] for 32-bit x and out and a bfloat16 w [heads, K, N], on the tensor cores with
+    32-bit accuracy: x is cut into three bfloat16 pieces whose products with w are exact and are added in 32-bit."""
+    _need(x, "head_matmul_split x", torch.float32); _need(w, "head_matmul_split w", torch.bfloat16); _need(out, "head_matmul_split out", torch.float32)
+    heads, K, N = w.shape
+    if x.shape[1] != heads * K or tuple(out.shape) != (x.shape[0], heads * N) or not head_matmul_split_supported(K, N, x.stride(0), out.stride(0)):
+        raise KernelError("head_matmul_split: shapes do not agree or are not served")
+    _call("latent", "ilb_head_matmul_split", _ptr(x), _i(x.stride(0)), _ptr(w), _ptr(out), _i(out.stride(0)), _i(x.shape[0]), _i(heads), _i(K),
+          _i(N), _i(K), _i(N), _stream(out))
+
+
 def latent_write_rot(proj: torch.Tensor, col0: int, rank: int, tail: int, rot: int, angles: Optional[torch.Tensor],
                      weight: Optional[torch.Tensor], eps: float, step, block_table: Optional[torch.Tensor],
                      cache: Optional[torch.Tensor], q_src: Optional[torch.Tensor] = None, q_dst: Optional[torch.Tensor] = None,
@@ -383,7 +399,7 @@ def dyt_add(y: torch.Tensor, norm, mult: float, x: torch.Tensor, next_norm=None,
 
 
 # --------------------------------------------------------------------------- linear recurrences over channels, gates
-LRU_CHUNK = 64             # tokens per chunk when a long portion's recurrence runs chunks side by side
+LRU_CHUNK = 32             # tokens per chunk when a long portion's recurrence runs chunks side by side
 LRU_CHUNK_FROM = 128       # portions from this many tokens on are cut into chunks
 
 
@@ -915,11 +931,12 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[
             accumulate: bool = False, max_ctas: int = 0, swiglu: bool = False, gate: str = "silu", glu=None) -> None:
     """out (+)= a @ w.T (+ bias) on tcgen05 tensor cores (see gemm_tcgen05.cu).  With
     `swiglu`, `w` holds blocks of 64 gate rows followed by their 64 up rows and `out` is
-    [M, N/2] = act(gate) * up, act = `gate` ("silu" or "relu")."""
+    [M, N/2] = act(gate) * up, act = `gate` ("silu" or "relu"); or, with `glu` = (limit, sharpness, up_offset), the
+    clamped unit a(min(gate, limit)) * (clamp(up, -limit, limit) + up_offset), a(g) = g * sigmoid(sharpness * g)."""
     if gate not in ("silu", "relu"):
         raise KernelError(f"gemm: the gated epilogue has no activation {gate!r}")
-    if glu is not None:
-        raise KernelError("gemm: the clamped gated unit is not in this product's epilogue")
+    if glu is not None and (not swiglu or float(glu[0]) <= 0):
+        raise KernelError("gemm: the clamped gated unit belongs to the gated epilogue and needs a positive limit")
     _need(a, "gemm a", torch.bfloat16); _need(w, "gemm w", torch.bfloat16); _need(out, "gemm out")
     _need(bias, "gemm bias", torch.float32)
     M, K = a.shape
@@ -930,11 +947,12 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[
     if accumulate and (out.dtype != torch.float32 or swiglu):
         raise KernelError("gemm: accumulation needs a 32-bit output and no SwiGLU epilogue")
     st = _tc_state(a.device)
-    mode = (3 if gate == "relu" else 2) if swiglu else (1 if accumulate else 0)
+    mode = (4 if glu is not None else 3 if gate == "relu" else 2) if swiglu else (1 if accumulate else 0)
+    limit, sharp, offset = glu if glu is not None else (0.0, 1.0, 0.0)
     _call("gemm_tcgen05", "ilb_gemm_tc", _ptr(a), _ptr(w), _ptr(bias), _ptr(out),
           _i(1 if out.dtype == torch.float32 else 0), _i(M), _i(N), _i(K), _i(a.stride(0)), _i(w.stride(0)),
           _i(out.stride(0)), _i(mode), _ptr(st.workspace), ctypes.c_longlong(st.floats),
-          _ptr(st.tickets), _i(st.n_tickets), _ptr(st.error), _i(max_ctas), _stream(out))
+          _ptr(st.tickets), _i(st.n_tickets), _ptr(st.error), _i(max_ctas), _f(limit), _f(sharp), _f(offset), _stream(out))
 
 
 def gemm_sums_in_memory(on: bool) -> None:

@@ -24,7 +24,7 @@
 using namespace ilb;
 
 constexpr int kLruThreads = 128;
-constexpr int kLruBatch = 4;          // tokens whose loads are in flight together
+constexpr int kLruBatch = 8;          // tokens whose loads are in flight together
 
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }

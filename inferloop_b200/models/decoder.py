@@ -32,6 +32,13 @@ class DecoderModel:
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
         self._weight_bytes = 0
+        # A block that always hands over to the same block may ready that block's input in its own last launch.
+        after: Dict[int, set] = {}
+        for a, b in zip(spec.run_order, spec.run_order[1:]):
+            after.setdefault(a.layer, set()).add(b.layer)
+        for layer, nxt in after.items():
+            if len(nxt) == 1 and hasattr(self.blocks[layer], "hand_over_to"):
+                self.blocks[layer].hand_over_to(self.blocks[next(iter(nxt))])
 
     # ------------------------------------------------------------------ weights
     def declare_weights(self) -> List[WeightDecl]:

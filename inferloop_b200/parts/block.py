@@ -168,7 +168,9 @@ class SandwichBlock(Block):
     """spec: hidden_size; residual_mult (default 1); tensor-name pieces mixer_prefix, ffn_prefix, mixer_norm, mixer_out_norm,
     ffn_norm, ffn_out_norm (under the layer prefix).  The layer's norm must be of kind `dyt`."""
 
-    ZEROED = "sandwich.zeroed"       # memo key: the sublayers' 32-bit buffer that the block before left at zero
+    # memo key: what the block before left ready: (the zeroed 32-bit buffer, the stream's shape, the block whose input
+    # the compute-dtype buffer already holds or None)
+    PREPARED = "sandwich.prepared"
 
     def __init__(self, spec, ctx, prefix: str = "", layer=None) -> None:
         super().__init__(spec, ctx, prefix)
@@ -184,7 +186,12 @@ class SandwichBlock(Block):
             if not isinstance(n, DynamicTanh):
                 raise ValueError("sandwich: the norms around a sublayer must be element-wise (kind 'dyt')")
 
-    PREPARED = ZEROED
+        self.successor = None
+
+    def hand_over_to(self, block) -> None:
+        """`block` always runs right after this one: this block's last launch norms the new stream for it too."""
+        if isinstance(block, SandwichBlock) and block.hidden == self.hidden:
+            self.successor = block
 
     @property
     def graph_safe(self) -> bool:
@@ -213,24 +220,28 @@ class SandwichBlock(Block):
         x = ws.buffer("block.normed", hidden.shape, self.ctx.dtype)          # what a sublayer reads
         y = ws.buffer("block.sublayer_out", hidden.shape, torch.float32)     # what it adds into
         memo = getattr(step, "memo", None)
-        zeroed = (y.data_ptr(), tuple(hidden.shape))
+        left = memo.pop(self.PREPARED, None) if memo is not None else None
         ops.scope("norm")
-        if memo is None or memo.pop(self.ZEROED, None) != zeroed:
+        if left is None or left[:2] != (y.data_ptr(), tuple(hidden.shape)):
             ops.cast_zero(hidden, x, y)
-        self.norm1.forward(hidden, x)
+            left = None
+        if left is None or left[2] != id(self):
+            self.norm1.forward(hidden, x)
         ops.scope("mixer")
         self.mixer.forward(x, y, step, cache)
         ops.scope("norm")
+        nxt = self.successor if memo is not None else None
+        handed = dict(next_norm=nxt.norm1.tensors, out=x) if nxt is not None else {}
         if self.has_ffn:
             ops.dyt_add(y, self.norm1b.tensors, self.mult, hidden, next_norm=self.norm2.tensors, out=x, zero=True)
             ops.scope("feed_forward")
             self.ffn.forward(x, y, step)
             ops.scope("norm")
-            ops.dyt_add(y, self.norm2b.tensors, self.mult, hidden, zero=True)
+            ops.dyt_add(y, self.norm2b.tensors, self.mult, hidden, zero=True, **handed)
         else:
-            ops.dyt_add(y, self.norm1b.tensors, self.mult, hidden, zero=True)
+            ops.dyt_add(y, self.norm1b.tensors, self.mult, hidden, zero=True, **handed)
         if memo is not None:
-            memo[self.ZEROED] = zeroed
+            memo[self.PREPARED] = (y.data_ptr(), tuple(hidden.shape), id(nxt) if nxt is not None else None)
 
 
 registry.register("block", "pre_norm", PreNormBlock)

@@ -74,7 +74,7 @@ class SwiGLU(FeedForward):
 
     def _fusable(self, dtype: torch.dtype) -> bool:
         """Whether the gated unit is taken in the tensor-core product's epilogue (gate and up rows interleaved)."""
-        return dtype == torch.bfloat16 and self.inter % 64 == 0 and self.hidden % 8 == 0 and self.glu is None
+        return dtype == torch.bfloat16 and self.inter % 64 == 0 and self.hidden % 8 == 0
 
     def scratch_bytes(self, tokens: int) -> int:
         size = torch.empty((), dtype=self.ctx.dtype).element_size()

@@ -8,7 +8,8 @@
 
 State per request: S [width] in 32-bit and the last taps - 1 inputs of the convolution.  The two input
 products are one product; the convolution is the state-space layer's (without its activation); the gates'
-block-diagonal products run in 32-bit (per-block product of csrc/latent.cu on 32-bit lanes); the gates, the
+block-diagonal products run with 32-bit accuracy (per-block products of csrc/latent.cu: on the tensor cores with the
+32-bit input cut into three exact bfloat16 pieces when the matrices are bfloat16, else on 32-bit lanes); the gates, the
 decay, the recurrence and the output gate are one kernel (csrc/recurrent.cu), chunked for long portions.
 
 `decayed_linear_attention` (lightning attention): q, k, v = silu(W h) per head, S_t = decay_h S_{t-1} + k_t v_t^T,
@@ -62,6 +63,7 @@ class GatedLinearRecurrence(Mixer):
         self.names = _names({"y": "y", "yb": "y.b", "x": "x", "xb": "x.b", "conv": "conv", "conv_bias": "conv.b", "ra": "ra",
                              "rab": "ra.b", "ri": "ri", "rib": "ri.b", "lam": "lam", "o": "o"}, spec, prefix, "the gated recurrence")
         self.w_in = self.b_in = self.conv_w = self.conv_b = self.w_gates = self.r_bias = self.i_bias = self.lam = self.w_o = None
+        self.split = False
 
     def declare_weights(self) -> List[WeightDecl]:
         n, W, H, B, bw = self.names, self.width, self.hidden, self.blocks, self.block_width
@@ -78,9 +80,13 @@ class GatedLinearRecurrence(Mixer):
         self.b_in = torch.cat([tensors[n["yb"]], tensors[n["xb"]]]).contiguous()
         self.conv_w = tensors[n["conv"]].contiguous()
         self.conv_b = tensors[n["conv_bias"]].contiguous()
-        # a block's two gate matrices side by side, [blocks, in, 2 out], in 32-bit: the gates are 32-bit arithmetic
-        ra, ri = tensors[n["ra"]].float(), tensors[n["ri"]].float()
+        # a block's two gate matrices side by side, [blocks, in, 2 out].  The gates are 32-bit arithmetic: bfloat16 matrices
+        # take the tensor-core product whose 32-bit input is cut into three exact pieces, others the 32-bit lanes
+        ra, ri = tensors[n["ra"]], tensors[n["ri"]]
         self.w_gates = torch.cat([ra.transpose(1, 2), ri.transpose(1, 2)], dim=2).contiguous()
+        self.split = ra.dtype == torch.bfloat16 and ops.head_matmul_split_supported(self.block_width, 2 * self.block_width, self.width, 2 * self.width)
+        if not self.split:
+            self.w_gates = self.w_gates.float()
         self.r_bias = tensors[n["rab"]].reshape(-1).contiguous()
         self.i_bias = tensors[n["rib"]].reshape(-1).contiguous()
         self.lam = tensors[n["lam"]].contiguous()
@@ -105,7 +111,10 @@ class GatedLinearRecurrence(Mixer):
         ops.ssm_conv(proj, W, W, self.conv_w, self.conv_b, cache.state["conv"], step, u, activation="none")
         ops.scope("recurrence.gates")
         gates = ws.buffer("lru.gates", (T, 2 * W), torch.float32)
-        ops.head_matmul(u, self.w_gates, gates)
+        if self.split:
+            ops.head_matmul_split(u, self.w_gates, gates)
+        else:
+            ops.head_matmul(u, self.w_gates, gates)
         ops.scope("recurrence.scan")
         gated = ws.buffer("lru.gated", (T, W), dt)
         ops.lru_scan(gates, u, proj, 0, self.r_bias, self.i_bias, self.lam, self.rate, cache.state["state"], gated, step,

@@ -338,6 +338,23 @@ def test_a_gate_a_head(heads, dv, pad, dtype):
         assert (od.double().cpu() - ref).abs().max() <= 2.0 ** -8 * ref.abs().max()
 
 
+@pytest.mark.parametrize("heads,K,N", [(1, 16, 8), (3, 48, 96), (4, 64, 128), (8, 256, 512), (2, 80, 24)])
+def test_per_block_product_on_the_tensor_cores_keeps_32_bit_accuracy(heads, K, N):
+    """32-bit rows times bfloat16 matrices, the rows cut into three exact bfloat16 pieces: as accurate as 32-bit
+    multiply-adds, for many tokens, few, and one; inputs of very different sizes in one row."""
+    from inferloop_b200.csrc import ops
+    g = torch.Generator().manual_seed(heads * K + N)
+    x = torch.randn(150, heads * K, generator=g) * torch.logspace(-3, 3, heads * K)
+    w = (torch.randn(heads, K, N, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    for T in (150, 64, 17, 1):
+        out = torch.empty(T, heads * N, dtype=torch.float32, device=DEV)
+        ops.head_matmul_split(x[:T].to(DEV), w.to(DEV), out)
+        xs = x.double()[:T].reshape(T, heads, K)
+        ref = torch.einsum("thk,hkn->thn", xs, w.double()).reshape(T, heads * N)
+        size = torch.einsum("thk,hkn->thn", xs.abs(), w.double().abs()).reshape(T, heads * N)      # what a 32-bit sum's error scales with
+        assert ((out.double().cpu() - ref).abs() <= 4e-7 * size + 1e-30).all(), f"{T} tokens: {float(((out.double().cpu() - ref).abs() / size).max()):.3e}"
+
+
 @pytest.mark.parametrize("width,blocks", [(24, 1), (60, 3), (256, 4), (35, 1), (1280, 5)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_gated_linear_recurrence_in_one_pass_in_chunks_and_in_portions(width, blocks, dtype):
@@ -352,7 +369,8 @@ def test_gated_linear_recurrence_in_one_pass_in_chunks_and_in_portions(width, bl
     u = [torch.randn(n, width, generator=g) for n in lens]
     u[0][0] *= 30.0                                                      # the first token's input stands out
     yraw = [torch.randn(n, width + 6, generator=g).to(dtype) for n in lens]
-    w = {"ra": 2 * torch.randn(blocks, bw, bw, generator=g) / math.sqrt(bw), "ri": 2 * torch.randn(blocks, bw, bw, generator=g) / math.sqrt(bw),
+    bf = lambda t: t.to(torch.bfloat16).float()            # (the matrices are stored in bfloat16 on one of the two paths)
+    w = {"ra": bf(2 * torch.randn(blocks, bw, bw, generator=g) / math.sqrt(bw)), "ri": bf(2 * torch.randn(blocks, bw, bw, generator=g) / math.sqrt(bw)),
          "ra.b": torch.randn(blocks, bw, generator=g), "ri.b": torch.randn(blocks, bw, generator=g), "lam": torch.linspace(-9.0, 1.0, width)}
     wd = {k: v.double() for k, v in w.items()}
     ref = []
@@ -380,7 +398,10 @@ def test_gated_linear_recurrence_in_one_pass_in_chunks_and_in_portions(width, bl
             x = torch.cat([u[s][a:b] for s, a, b in parts]).to(DEV)
             yy = torch.cat([yraw[s][a:b] for s, a, b in parts]).to(DEV)
             gates = torch.empty(x.shape[0], 2 * width, dtype=torch.float32, device=DEV)
-            ops.head_matmul(x, gates_w, gates)
+            if dtype == torch.bfloat16 and ops.head_matmul_split_supported(bw, 2 * bw, width, 2 * width):
+                ops.head_matmul_split(x, gates_w.to(torch.bfloat16), gates)
+            else:
+                ops.head_matmul(x, gates_w, gates)
             out = torch.empty(x.shape[0], width, dtype=dtype, device=DEV)
             chunk = {"one pass": 0, "chunks": 64, "portions": None}[mode]
             ops.lru_scan(gates, x, yy, 3, f32(w["ra.b"].reshape(-1)), f32(w["ri.b"].reshape(-1)), f32(w["lam"]), plain.DECAY_RATE, state, out,
