@@ -2,7 +2,7 @@
 statement in plain_zebivik.py.  The configurations are in zebivik_cases.py: K (odd sizes, exact kernels, groups of
 experts of which two of three stay, a layer without feed-forward), L (the tensor-core kernels' sizes, values as wide
 as keys and narrower, one group of four kept), M (everything plural is one, sizes that are multiples of nothing),
-N (recurrences only: no pages, only state slots).
+N (recurrences only: no pages, only state slots), P (heads and values of 128, dense units only).
 """
 import json
 import math
@@ -20,7 +20,7 @@ from helpers import ROOT, Trace, assert_close, check_trace, random_tokens, run_t
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
-ENGINE_CASES = [(n, d) for n in ("K", "L", "M", "N") for d in ("float32", "bfloat16")]
+ENGINE_CASES = [(n, d) for n in ("K", "L", "M", "N", "P") for d in ("float32", "bfloat16")]
 
 
 @pytest.fixture(scope="module")

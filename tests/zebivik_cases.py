@@ -92,7 +92,15 @@ CONFIG_N = model(150, 64, 1e-5, 0.5, [
     layer(rglru(64, 2, 4), moe(4, 2, 32, 1.5, groups=(2, 1))),
     layer(rglru(96, 3, 2), dense(64, 1.0)),
 ])
-CASES = {"K": (CONFIG_K, 41, 4), "L": (CONFIG_L, 42, 16), "M": (CONFIG_M, 43, 8), "N": (CONFIG_N, 44, 16)}     # config, seed, page size
+# P: heads of 128 with values of 128 (the tcgen05 prefill attention and the decode attention with its input stage inside at
+# their widest), half of each head rotated with rescaled frequencies, groups of four heads; a dense unit of 64-row blocks (the
+# clamped unit inside the tensor-core product).
+CONFIG_P = model(500, 128, 2e-6, 0.6, [
+    layer(parallel(softmax_branch(4, 1, 128, 128, 0.088, rot=(30000.0, 64, (4.0, 1.0, 2.0, 256.0))), linear_branch(2, 16, 64, (0.9, 0.998)), 1.1, 0.6),
+          dense(128, 1.25)),
+    layer(rglru(128, 2, 4), dense(192, 0.7)),
+], softcap=12.0)
+CASES = {"P": (CONFIG_P, 45, 16), "K": (CONFIG_K, 41, 4), "L": (CONFIG_L, 42, 16), "M": (CONFIG_M, 43, 8), "N": (CONFIG_N, 44, 16)}     # config, seed, page size
 
 _FOLDERS: Dict[tuple, str] = {}
 _PLAIN: Dict[tuple, "Plain"] = {}
@@ -114,6 +122,8 @@ def _sharpen(name: str, t: torch.Tensor) -> torch.Tensor:
         return t.float() * 4.0
     if name.endswith(".left.g"):
         return t.float() * 6.0
+    if name.endswith((".left.q", ".left.k")):       # a softmax that picks few keys, wherever they lie
+        return t.float() * 2.0
     if name == "embed":
         return t.float() * 4.0
     if name == "head":
