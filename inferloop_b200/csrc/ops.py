@@ -722,7 +722,9 @@ def qk_norm_rope_cache(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: Optiona
     NORM_UNWEIGHTED.  `v_first` [T, nkv * dv]: with `v_keep` it receives this layer's values;
     with `v_lambda` (a device scalar) the values become (1 - lambda) v + lambda v_first first."""
     dv = d if dv is None else int(dv)
-    _need(qkv, "qkv"); _need(q_out, "q_out", qkv.dtype)
+    _need(qkv, "qkv", contiguous=False); _need(q_out, "q_out", qkv.dtype)
+    if qkv.stride(1) != 1 or qkv.shape[1] < (nq + nkv) * d + nkv * dv:
+        raise KernelError("qk_norm_rope_cache: the projection's rows must hold q | k | v side by side")
     _need(q_weight, "q_norm weight", torch.float32); _need(k_weight, "k_norm weight", torch.float32)
     _need(rope, "rope table", torch.float32); _need(positions, "positions", torch.int32)
     _need(seq_of_token, "seq_of_token", torch.int32); _need(block_table, "block table", torch.int32)
@@ -746,7 +748,7 @@ def qk_norm_rope_cache(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: Optiona
           _ptr(q_weight), _ptr(k_weight), _f(eps), _ptr(rope), _i(rotary_dim), _ptr(positions),
           _ptr(seq_of_token), _ptr(block_table), _i(max_blocks), _i(page_size), _i(num_pages),
           _ptr(k_cache), _ptr(v_cache), _i(cache_code), _i(T), _i(nq), _i(nkv), _i(d), _i(dv),
-          _i(qkv.shape[1]), _i(q_out.shape[1]), _i(mode), _i(v_mode), _ptr(v_lambda), _ptr(v_first if v_mode else None),
+          _i(qkv.stride(0)), _i(q_out.shape[1]), _i(mode), _i(v_mode), _ptr(v_lambda), _ptr(v_first if v_mode else None),
           _stream(qkv))
 
 
@@ -1145,14 +1147,17 @@ def attention_decode_fused(qkv, out, q_weight, k_weight, eps, rope_table, k_cach
         if v_first is None or tuple(v_first.shape) != (qkv.shape[0], nkv * d) or (v_keep and v_lambda is not None):
             raise KernelError("value mixing needs first values [tokens, nkv * d], and either keeps or mixes them")
         v_mode = 1 if v_keep else 2
-    for t, w in ((qkv, "qkv"), (out, "out"), (k_cache, "k cache"), (v_cache, "v cache")):
+    _need(qkv, "attention qkv", torch.bfloat16, contiguous=False)
+    if qkv.stride(1) != 1 or qkv.shape[1] < (nq + 2 * nkv) * d:
+        raise KernelError("attention_decode_fused: the projection's rows must hold q | k | v side by side")
+    for t, w in ((out, "out"), (k_cache, "k cache"), (v_cache, "v cache")):
         _need(t, "attention " + w, torch.bfloat16)
     for t, w in ((q_weight, "q norm weight"), (k_weight, "k norm weight"), (rope_table, "rope table")):
         if t is not None:
             _need(t, "attention " + w, torch.float32)
     num_pages, _, page_size, _ = k_cache.shape
     st = _tc_state(qkv.device)
-    _call("attention_decode", "ilb_attention_decode_fused", _ptr(qkv), _i(qkv.shape[1]), _ptr(q_weight), _ptr(k_weight),
+    _call("attention_decode", "ilb_attention_decode_fused", _ptr(qkv), _i(qkv.stride(0)), _ptr(q_weight), _ptr(k_weight),
           _f(eps if eps and eps > 0 else 1e-6), _ptr(rope_table), _i(mode), _i(d if rotary_dim is None else rotary_dim), _i(v_mode),
           _ptr(v_first if v_mode else None), _ptr(v_lambda if v_mode == 2 else None), _i(1 if write_kv else 0), _ptr(out),
           _ptr(k_cache), _ptr(v_cache), _ptr(positions),

@@ -183,14 +183,29 @@ class GQAttention(Mixer):
         return tokens * ((width + self.nq * (self.d + self.dv) + kept) * size + self.rotary_dim * 4)
 
     # ------------------------------------------------------------------ run
+    def input_rows(self):
+        """(matrix, bias or None) of the one product this mixer starts with: a mixer that runs beside others can have its
+        rows stacked with theirs (see `forward_projected`).  The matrix may be replaced by a view of the stacked one."""
+        return self.w_qkv, self.b_qkv
+
+    def take_input_rows(self, rows: torch.Tensor) -> None:
+        """The same matrix as a view of the stacked one: no second copy is kept."""
+        self.w_qkv = rows
+
     def forward(self, x: torch.Tensor, residual: torch.Tensor, step, cache) -> None:
         T = x.shape[0]
         ws, dt = self.ctx.workspace, self.ctx.dtype
-        gate_col0 = (self.nq + self.nkv) * self.d + self.nkv * self.dv      # the heads' gate logits ride behind q | k | v
-        width = gate_col0 + self.gate_rows
+        width = (self.nq + self.nkv) * self.d + self.nkv * self.dv + self.gate_rows
         qkv = ws.buffer("attn.qkv", (T, width), dt)
         ops.scope("attention.qkv_projection")
         linear(x, self.w_qkv, qkv, self.b_qkv)
+        self.forward_projected(qkv, residual, step, cache)
+
+    def forward_projected(self, qkv: torch.Tensor, residual: torch.Tensor, step, cache) -> None:
+        """The mixer from its projection's output on: `qkv` [T, q | k | v (| gates)], rows of any stride."""
+        T = qkv.shape[0]
+        ws, dt = self.ctx.workspace, self.ctx.dtype
+        gate_col0 = (self.nq + self.nkv) * self.d + self.nkv * self.dv      # the heads' gate logits ride behind q | k | v
         table = step.block_tables[cache.group]
         ops.scope("attention.position_table")
         rope = self.position.table(step)

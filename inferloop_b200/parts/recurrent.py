@@ -165,11 +165,24 @@ class DecayedLinearAttention(Mixer):
         return (tokens * ((self.channels + 2 * self.inner) * size + (self.channels + self.inner) * 4)
                 + chunks * self.heads * (self.d * self.dv + 1) * 4)
 
+    def input_rows(self):
+        """(matrix, bias or None) of the one product this mixer starts with (see `forward_projected`)."""
+        return self.w_in, None
+
+    def take_input_rows(self, rows: torch.Tensor) -> None:
+        """The same matrix as a view of the stacked one: no second copy is kept."""
+        self.w_in = rows
+
     def forward(self, x: torch.Tensor, residual: torch.Tensor, step, cache) -> None:
         T, ws, dt = x.shape[0], self.ctx.workspace, self.ctx.dtype
         proj = ws.buffer("linattn.proj", (T, self.channels + self.inner), dt)
         ops.scope("linear_attention.in_projection")
         linear(x, self.w_in, proj)
+        self.forward_projected(proj, residual, step, cache)
+
+    def forward_projected(self, proj: torch.Tensor, residual: torch.Tensor, step, cache) -> None:
+        """The mixer from its projection's output on: `proj` [T, v | k | q | gate], rows of any stride."""
+        T, ws, dt = proj.shape[0], self.ctx.workspace, self.ctx.dtype
         ops.scope("linear_attention.activation")
         act = ws.buffer("linattn.act", (T, self.channels), torch.float32)
         ops.silu_rows(proj, self.channels, act)
@@ -186,7 +199,9 @@ class DecayedLinearAttention(Mixer):
 
 class ParallelMixers(Mixer):
     """spec: `branches` = ((sub-prefix, PartSpec of role mixer), ...).  Every branch reads the block's input and adds
-    into the block's output; a branch's constant on its output is its own parameter (`out_scale`)."""
+    into the block's output; a branch's constant on its output is its own parameter (`out_scale`).  Branches that start
+    with one product of the input each (`input_rows` / `forward_projected`) share ONE product: their matrices are
+    stacked at load (each branch keeps a view of its rows) and every branch reads its columns of the result."""
 
     def __init__(self, spec, ctx, prefix: str = "") -> None:
         super().__init__(spec, ctx, prefix)
@@ -194,6 +209,8 @@ class ParallelMixers(Mixer):
         if not branches:
             raise ValueError("parallel: no branches")
         self.parts = [registry.build("mixer", part, ctx, prefix + sub) for sub, part in branches]
+        self.w_all = self.b_all = None
+        self.columns = []
         if sum(1 for p in self.parts if p.cache_needs().paged is not None) > 1:
             raise ValueError("parallel: at most one branch may keep keys and values in pages")
 
@@ -207,6 +224,24 @@ class ParallelMixers(Mixer):
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         for p in self.parts:
             p.bind(tensors)
+        self.w_all = self.b_all = None
+        self.columns = []
+        if len(self.parts) < 2 or not all(hasattr(p, "input_rows") and hasattr(p, "forward_projected") for p in self.parts):
+            return
+        rows = [p.input_rows() for p in self.parts]
+        # every branch's columns start on a 16-byte boundary of the shared result
+        if any(w.shape[0] % 8 for w, _ in rows) or len({(w.dtype, w.shape[1]) for w, _ in rows}) != 1:
+            return
+        self.w_all = torch.cat([w for w, _ in rows], dim=0).contiguous()
+        if any(b is not None for _, b in rows):
+            self.b_all = torch.cat([b if b is not None else torch.zeros(w.shape[0], dtype=torch.float32, device=w.device)
+                                    for w, b in rows]).contiguous()
+        at = 0
+        for p, (w, _) in zip(self.parts, rows):
+            self.columns.append((at, at + w.shape[0]))
+            if hasattr(p, "take_input_rows"):
+                p.take_input_rows(self.w_all[at:at + w.shape[0]])
+            at += w.shape[0]
 
     def cache_needs(self) -> CacheNeeds:
         paged, slots = None, []
@@ -217,13 +252,22 @@ class ParallelMixers(Mixer):
         return CacheNeeds(paged=paged, slots=tuple(slots))
 
     def scratch_bytes(self, tokens: int) -> int:
-        return sum(p.scratch_bytes(tokens) for p in self.parts)
+        return sum(p.scratch_bytes(tokens) for p in self.parts)          # (the shared result is the branches' own, side by side)
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor, step, cache) -> None:
+        proj = None
+        if self.w_all is not None:
+            proj = self.ctx.workspace.buffer("parallel.proj", (x.shape[0], self.w_all.shape[0]), self.ctx.dtype)
+            ops.scope("parallel.in_projection")
+            linear(x, self.w_all, proj, self.b_all)
         for i, p in enumerate(self.parts):
             tag = f"{i}."
             own = dataclasses.replace(cache, state={k[len(tag):]: v for k, v in cache.state.items() if k.startswith(tag)})
-            p.forward(x, residual, step, own)
+            if proj is not None:
+                a, b = self.columns[i]
+                p.forward_projected(proj[:, a:b], residual, step, own)
+            else:
+                p.forward(x, residual, step, own)
 
 
 registry.register("mixer", "gated_linear_recurrence", GatedLinearRecurrence)
