@@ -176,9 +176,37 @@ silu_rows_kernel(const TI* __restrict__ x, int ld, float* __restrict__ out, int 
   }
 }
 
+// Eight bfloat16 elements a thread and access (16 bytes in, 32 out).
+__global__ void __launch_bounds__(256)
+silu_rows_vec_kernel(const __nv_bfloat16* __restrict__ x, int ld, float* __restrict__ out, int rows, int width8) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  const size_t n = (size_t)rows * width8;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / width8, c = (i % width8) * 8;
+    const uint4 v = *reinterpret_cast<const uint4*>(x + r * ld + c);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    float o[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      o[2 * j] = silu_f(__uint_as_float(w[j] << 16));
+      o[2 * j + 1] = silu_f(__uint_as_float(w[j] & 0xFFFF0000u));
+    }
+    float4* dst = reinterpret_cast<float4*>(out + r * (size_t)width8 * 8 + c);
+    dst[0] = make_float4(o[0], o[1], o[2], o[3]);
+    dst[1] = make_float4(o[4], o[5], o[6], o[7]);
+  }
+}
+
 ILB_EXPORT int ilb_silu_rows(const void* x, int dtype, int ld, float* out, int rows, int width, cudaStream_t stream) {
   ILB_REQUIRE(rows >= 0 && width > 0 && ld >= width, "silu_rows: bad sizes");
   if (rows == 0) return 0;
+  if (dtype == kBF16 && width % 8 == 0 && ld % 8 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)out % 16 == 0)) {
+    const size_t n8 = (size_t)rows * (width / 8);
+    const int blocks8 = (int)((n8 + 255) / 256 < 148 * 16 ? (n8 + 255) / 256 : 148 * 16);
+    ilb::launch(silu_rows_vec_kernel, dim3(blocks8), dim3(256), 0, stream, (const __nv_bfloat16*)x, ld, out, rows, width / 8);
+    return check_launch("silu_rows");
+  }
   const size_t n = (size_t)rows * width;
   const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
   if (dtype == kF32) ilb::launch(silu_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, ld, out, rows, width);
@@ -237,6 +265,29 @@ head_gate_kernel(TI* __restrict__ o, const TI* __restrict__ gate, int ld_gate, i
   }
 }
 
+// Eight bfloat16 elements of one head a thread and access.
+__global__ void __launch_bounds__(256)
+head_gate_vec_kernel(__nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ gate, int ld_gate, int rows, int heads, int dv8,
+                     float scale) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  const int per_row = heads * dv8;
+  const size_t n = (size_t)rows * per_row;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / per_row;
+    const int h = (int)(i % per_row) / dv8;
+    const float g = sigmoid_f(__bfloat162float(gate[r * ld_gate + h])) * scale;
+    uint4 v = *reinterpret_cast<const uint4*>(o + i * 8);
+    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(w[j] << 16) * g, __uint_as_float(w[j] & 0xFFFF0000u) * g);
+      w[j] = *reinterpret_cast<const uint32_t*>(&p);
+    }
+    *reinterpret_cast<uint4*>(o + i * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 // o: [rows, heads * dv] of `dtype`, in place; gate: [rows, ld_gate] of `dtype`, head h's logit at column h of the
 // pointer given.
 ILB_EXPORT int ilb_head_gate(void* o, const void* gate, int dtype, int ld_gate, int rows, int heads, int dv, float scale,
@@ -244,6 +295,13 @@ ILB_EXPORT int ilb_head_gate(void* o, const void* gate, int dtype, int ld_gate, 
   ILB_REQUIRE(rows >= 0 && heads > 0 && dv > 0 && ld_gate >= heads, "head_gate: bad sizes");
   if (rows == 0) return 0;
   const size_t n = (size_t)rows * heads * dv;
+  if (dtype == kBF16 && dv % 8 == 0 && ((uintptr_t)o % 16 == 0)) {
+    const size_t n8 = n / 8;
+    const int blocks8 = (int)((n8 + 255) / 256 < 148 * 16 ? (n8 + 255) / 256 : 148 * 16);
+    ilb::launch(head_gate_vec_kernel, dim3(blocks8), dim3(256), 0, stream, (__nv_bfloat16*)o, (const __nv_bfloat16*)gate, ld_gate, rows, heads,
+                dv / 8, scale);
+    return check_launch("head_gate");
+  }
   const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
   if (dtype == kF32) ilb::launch(head_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)o, (const float*)gate, ld_gate, rows, heads, dv, scale);
   else if (dtype == kBF16)

@@ -235,6 +235,42 @@ dyt_add_kernel(float* __restrict__ y, DytWeights n1, float mult, float* __restri
   }
 }
 
+// Four elements a thread and access: the width a multiple of four and every pointer on a 16-byte boundary.
+template <typename TO>
+__global__ void __launch_bounds__(kNormThreads)
+dyt_add_vec_kernel(float4* __restrict__ y, DytWeights n1, float mult, float4* __restrict__ x, DytWeights n2, TO* __restrict__ out,
+                   int zero, size_t total4, int width4) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  const float a1 = n1.alpha[0], a2 = out != nullptr ? n2.alpha[0] : 0.f;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (size_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % width4);
+    const float4 yv = y[i], xv = x[i];
+    const float4 g = reinterpret_cast<const float4*>(n1.g)[c], b = reinterpret_cast<const float4*>(n1.b)[c];
+    float4 v;
+    v.x = fmaf(mult, fmaf(tanhf(a1 * yv.x), g.x, b.x), xv.x);
+    v.y = fmaf(mult, fmaf(tanhf(a1 * yv.y), g.y, b.y), xv.y);
+    v.z = fmaf(mult, fmaf(tanhf(a1 * yv.z), g.z, b.z), xv.z);
+    v.w = fmaf(mult, fmaf(tanhf(a1 * yv.w), g.w, b.w), xv.w);
+    x[i] = v;
+    if (out != nullptr) {
+      const float4 g2 = reinterpret_cast<const float4*>(n2.g)[c], b2 = reinterpret_cast<const float4*>(n2.b)[c];
+      const float4 o = make_float4(fmaf(tanhf(a2 * v.x), g2.x, b2.x), fmaf(tanhf(a2 * v.y), g2.y, b2.y),
+                                   fmaf(tanhf(a2 * v.z), g2.z, b2.z), fmaf(tanhf(a2 * v.w), g2.w, b2.w));
+      if constexpr (sizeof(TO) == 4) {
+        reinterpret_cast<float4*>(out)[i] = o;
+      } else {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(o.x, o.y), hi = __floats2bfloat162_rn(o.z, o.w);
+        uint2 pk;
+        pk.x = *reinterpret_cast<uint32_t*>(&lo);
+        pk.y = *reinterpret_cast<uint32_t*>(&hi);
+        reinterpret_cast<uint2*>(out)[i] = pk;
+      }
+    }
+    if (zero) y[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
 static inline int dyt_blocks(size_t total) {
   const size_t want = (total + kNormThreads - 1) / kNormThreads;
   return (int)(want < 148 * 16 ? want : 148 * 16);
@@ -262,6 +298,19 @@ ILB_EXPORT int ilb_dyt_add(float* y, const float* alpha1, const float* g1, const
   if (rows == 0) return 0;
   const size_t total = (size_t)rows * width;
   const DytWeights n1{alpha1, g1, b1}, n2{alpha2, g2, b2};
+  auto aligned = [](const void* p) { return (uintptr_t)p % 16 == 0; };
+  if (width % 4 == 0 && aligned(y) && aligned(x) && aligned(g1) && aligned(b1) && aligned(out) &&
+      (out == nullptr || (aligned(g2) && aligned(b2)))) {
+    const size_t total4 = total / 4;
+    if (out == nullptr || out_dtype == kF32)
+      ilb::launch(dyt_add_vec_kernel<float>, dim3(dyt_blocks(total4)), dim3(kNormThreads), 0, stream, (float4*)y, n1, mult, (float4*)x, n2,
+                  (float*)out, zero, total4, width / 4);
+    else if (out_dtype == kBF16)
+      ilb::launch(dyt_add_vec_kernel<__nv_bfloat16>, dim3(dyt_blocks(total4)), dim3(kNormThreads), 0, stream, (float4*)y, n1, mult, (float4*)x,
+                  n2, (__nv_bfloat16*)out, zero, total4, width / 4);
+    else return fail("dyt_add: unknown dtype %d", out_dtype);
+    return check_launch("dyt_add");
+  }
   if (out == nullptr || out_dtype == kF32)
     ilb::launch(dyt_add_kernel<float>, dim3(dyt_blocks(total)), dim3(kNormThreads), 0, stream, y, n1, mult, x, n2, (float*)out, zero, total, width);
   else if (out_dtype == kBF16)

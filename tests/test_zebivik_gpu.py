@@ -468,6 +468,18 @@ def test_linear_attention_with_a_constant_decay(heads, d, dv, decay):
         assert float(state[1].min()) == 5.0
 
 
+@pytest.mark.parametrize("width,extra", [(24, 8), (30, 3), (256, 64), (1000, 24)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_silu_of_a_projections_leading_columns(width, extra, dtype):
+    """Rows on 16-byte boundaries (eight elements an access) and others; the columns behind the leading ones are left alone."""
+    from inferloop_b200.csrc import ops
+    g = torch.Generator().manual_seed(width)
+    x = (3 * torch.randn(37, width + extra, generator=g)).to(dtype)
+    out = torch.full((37, width), 7.0, dtype=torch.float32, device=DEV)
+    ops.silu_rows(x.to(DEV), width, out)
+    assert_close(out, plain.silu(x.double()[:, :width]), "float32", "silu of rows")
+
+
 @pytest.mark.parametrize("taps,channels", [(1, 40), (2, 130), (4, 256), (5, 33)])
 def test_short_convolution_without_activation(taps, channels):
     """The state-space layer's convolution with its activation switched off: whole and in portions through the slot."""
