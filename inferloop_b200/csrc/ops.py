@@ -399,7 +399,7 @@ def dyt_add(y: torch.Tensor, norm, mult: float, x: torch.Tensor, next_norm=None,
 
 
 # --------------------------------------------------------------------------- linear recurrences over channels, gates
-LRU_CHUNK = 32             # tokens per chunk when a long portion's recurrence runs chunks side by side
+LRU_CHUNK = 16             # tokens per chunk when a long portion's recurrence runs chunks side by side
 LRU_CHUNK_FROM = 128       # portions from this many tokens on are cut into chunks
 
 

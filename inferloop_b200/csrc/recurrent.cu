@@ -87,15 +87,21 @@ lru_scan_kernel(const LruParams p) {
       uu[j] = p.u[(size_t)t * p.W + c];
       yy[j] = p.pass == kPassLocal ? 0.f : to_float(yraw[(size_t)t * p.ld]);
     }
+    // the decays and inputs of the batch do not wait on one another; only the multiply-adds below form a chain
+    float a[kLruBatch], in[kLruBatch];
+#pragma unroll
+    for (int j = 0; j < kLruBatch; ++j) {
+      const float log_a = neg * sigmoid_f(gr[j] + rb);
+      a[j] = expf(log_a);
+      in[j] = sqrtf(-expm1f(2.0f * log_a)) * sigmoid_f(gi[j] + ib) * uu[j];
+      if (p.pass != kPassLocal) yy[j] = gelu_tanh_f(yy[j]);
+    }
 #pragma unroll
     for (int j = 0; j < kLruBatch; ++j) {
       if (t0 + j < end) {
-        const float log_a = neg * sigmoid_f(gr[j] + rb);
-        const float a = expf(log_a);
-        const float in = sqrtf(-expm1f(2.0f * log_a)) * sigmoid_f(gi[j] + ib) * uu[j];
-        S = fmaf(a, S, in);
-        if (p.pass == kPassLocal) decay *= a;
-        else out[(size_t)(t0 + j) * p.W] = from_float<TI>(S * gelu_tanh_f(yy[j]));
+        S = fmaf(a[j], S, in[j]);
+        if (p.pass == kPassLocal) decay *= a[j];
+        else out[(size_t)(t0 + j) * p.W] = from_float<TI>(S * yy[j]);
       }
     }
   }
@@ -121,11 +127,21 @@ lru_carry_kernel(float* __restrict__ state, float* __restrict__ chunk_state, con
   const int n = (cu_q[seq + 1] - cu_q[seq] + chunk - 1) / chunk;
   const int slot = slots[seq];
   float run = slot >= 0 ? state[(size_t)slot * W + c] : 0.f;
-  for (int k = first; k < first + n; ++k) {
-    const size_t at = (size_t)k * W + c;
-    const float local = chunk_state[at];
-    chunk_state[at] = run;
-    run = fmaf(chunk_decay[at], run, local);
+  for (int k0 = first; k0 < first + n; k0 += kLruBatch) {      // the loads of a batch of chunks are in flight together
+    float local[kLruBatch], dec[kLruBatch];
+#pragma unroll
+    for (int j = 0; j < kLruBatch; ++j) {
+      const size_t at = (size_t)min(k0 + j, first + n - 1) * W + c;
+      local[j] = chunk_state[at];
+      dec[j] = chunk_decay[at];
+    }
+#pragma unroll
+    for (int j = 0; j < kLruBatch; ++j) {
+      if (k0 + j < first + n) {
+        chunk_state[(size_t)(k0 + j) * W + c] = run;
+        run = fmaf(dec[j], run, local[j]);
+      }
+    }
   }
   if (slot >= 0 && n > 0) state[(size_t)slot * W + c] = run;
 }
