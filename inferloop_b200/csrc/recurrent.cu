@@ -4,7 +4,7 @@
 //   lru_scan    a gated linear recurrence over channels (the real-gated linear recurrent unit): with the
 //               gates' logits gr, gi (a block-diagonal product of the convolved input u, made elsewhere),
 //                 r = sigmoid(gr + br),  i = sigmoid(gi + bi),  log a = -rate * r * softplus(lam),  a = exp(log a)
-//                 S_t = a S_{t-1} + sqrt(1 - a^2) * i * u_t          (1 - a^2 as -expm1(2 log a): no cancellation)
+//                 S_t = a S_{t-1} + sqrt(1 - a^2) * i * u_t          (1 - a^2 as -expm1(2 log a), or a series near zero: no cancellation)
 //                 out_t = S_t * gelu_tanh(y_t)
 //               One thread a (sequence or chunk, channel).  A long portion is cut into chunks that run side by
 //               side in three passes, as ssm.cu does: every chunk from zero with the product of its decays, the
@@ -31,6 +31,32 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x));
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 __device__ __forceinline__ float gelu_tanh_f(float z) {
   return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// The scan's element-wise functions in two forms.  Exact: the library's functions (the 32-bit path).  Fast: the hardware's
+// exponential and reciprocal (a few units in the last place), for rows that are stored in bfloat16 behind them; still 32-bit
+// arithmetic, and 1 - exp(x) keeps its accuracy near zero through a short series.
+template <bool FAST> __device__ __forceinline__ float exp_t(float x) { return FAST ? __expf(x) : expf(x); }
+template <bool FAST> __device__ __forceinline__ float sigmoid_t(float x) {
+  return FAST ? __fdividef(1.0f, 1.0f + __expf(-x)) : 1.0f / (1.0f + expf(-x));
+}
+// 1 - exp(x) for x <= 0
+template <bool FAST> __device__ __forceinline__ float one_minus_exp_t(float x, float exp_x) {
+  if (!FAST) return -expm1f(x);
+  if (x < -0.25f) return 1.0f - exp_x;
+  float s = fmaf(x, 1.0f / 7.0f, 1.0f);
+  s = fmaf(x * (1.0f / 6.0f), s, 1.0f);
+  s = fmaf(x * (1.0f / 5.0f), s, 1.0f);
+  s = fmaf(x * (1.0f / 4.0f), s, 1.0f);
+  s = fmaf(x * (1.0f / 3.0f), s, 1.0f);
+  s = fmaf(x * (1.0f / 2.0f), s, 1.0f);
+  return -x * s;
+}
+template <bool FAST> __device__ __forceinline__ float gelu_tanh_t(float z) {
+  if (!FAST) return gelu_tanh_f(z);
+  const float w = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+  const float th = 1.0f - __fdividef(2.0f, __expf(2.0f * w) + 1.0f);      // tanh(w); exp overflows to inf: 1 - 0
+  return 0.5f * z * (1.0f + th);
 }
 
 __device__ __forceinline__ bool find_tile(const int* __restrict__ cu_q, int n_seqs, int tile, int b, int& seq, int& index) {
@@ -71,6 +97,7 @@ lru_scan_kernel(const LruParams p) {
   const int begin = tok0 + ci * p.chunk, end = tok0 + min(q_len, (ci + 1) * p.chunk);
   const int slot = p.slots[seq];
   const int gcol = (c / p.bw) * 2 * p.bw + c % p.bw;
+  constexpr bool FAST = sizeof(TI) == 2;
   const float rb = p.rb[c], ib = p.ib[c], neg = -p.rate * softplus_f(p.lam[c]);
   const TI* yraw = reinterpret_cast<const TI*>(p.proj) + p.y_col0 + c;
   TI* out = reinterpret_cast<TI*>(p.out) + c;
@@ -91,10 +118,12 @@ lru_scan_kernel(const LruParams p) {
     float a[kLruBatch], in[kLruBatch];
 #pragma unroll
     for (int j = 0; j < kLruBatch; ++j) {
-      const float log_a = neg * sigmoid_f(gr[j] + rb);
-      a[j] = expf(log_a);
-      in[j] = sqrtf(-expm1f(2.0f * log_a)) * sigmoid_f(gi[j] + ib) * uu[j];
-      if (p.pass != kPassLocal) yy[j] = gelu_tanh_f(yy[j]);
+      if (t0 + j < end) {
+        const float log_a = neg * sigmoid_t<FAST>(gr[j] + rb);
+        a[j] = exp_t<FAST>(log_a);
+        in[j] = sqrtf(one_minus_exp_t<FAST>(2.0f * log_a, a[j] * a[j])) * sigmoid_t<FAST>(gi[j] + ib) * uu[j];
+        if (p.pass != kPassLocal) yy[j] = gelu_tanh_t<FAST>(yy[j]);
+      }
     }
 #pragma unroll
     for (int j = 0; j < kLruBatch; ++j) {
