@@ -498,7 +498,7 @@ def test_short_convolution_without_activation(taps, channels):
         at += n
 
 
-@pytest.mark.parametrize("experts,top,groups,keep", [(6, 2, 3, 2), (8, 3, 2, 1), (8, 2, 4, 1), (1, 1, 1, 1), (12, 4, 1, 1), (64, 6, 8, 3), (40, 8, 4, 4)])
+@pytest.mark.parametrize("experts,top,groups,keep", [(6, 2, 3, 2), (10, 3, 2, 1), (8, 2, 4, 1), (1, 1, 1, 1), (12, 4, 1, 1), (64, 6, 8, 3), (40, 8, 4, 4)])
 def test_routing_with_a_ranking_correction_and_groups(experts, top, groups, keep):
     """Softmax scores; the ranking adds a correction, the weights do not; a group ranks by its best member and only the
     best groups' experts can win, also when every ranking score is negative; weights divided by their sum and scaled."""

@@ -71,13 +71,13 @@ CONFIG_K = model(203, 72, 1e-5, 0.7, [
 ], softcap=6.0)
 # L: the sizes the tensor-core kernels take: heads of 64 with values of 64 (tcgen05 prefill and cluster decode attention) and
 # heads of 128 with values of 64 (the exact kernel under bfloat16 products), a full rotation without rescaling and a partial one
-# with it, linear attention states of 64 x 64 and 128 x 32, a recurrence of 256 channels in 4 blocks; experts of 64 (the grouped
+# with it, linear attention states of 64 x 64 and 128 x 32, a recurrence of 256 channels in 2 blocks; experts of 64 (the grouped
 # tcgen05 product) in four groups of which one stays; no cap on the logits; the multiplier one.
 CONFIG_L = model(1000, 256, 1e-6, 1.0, [
-    layer(rglru(256, 4, 4), dense(512, 7.0)),
+    layer(rglru(256, 2, 4), dense(512, 7.0)),
     layer(parallel(softmax_branch(8, 2, 64, 64, 0.125, rot=(10000.0, 64, None)), linear_branch(4, 64, 64, (0.5, 0.9, 0.99, 0.999)), 1.0, 1.0),
           moe(8, 2, 64, 1.0, groups=(4, 1), shared=128)),
-    layer(parallel(softmax_branch(2, 1, 128, 64, 0.09, rot=(500000.0, 32, (8.0, 1.0, 4.0, 64.0))), linear_branch(2, 128, 32, (0.97, 0.6)), 0.5, 2.0),
+    layer(parallel(softmax_branch(2, 1, 128, 64, 0.09, rot=(500000.0, 32, (6.0, 1.0, 3.0, 64.0))), linear_branch(2, 128, 32, (0.97, 0.6)), 0.5, 2.0),
           moe(4, 1, 128, 2.5)),
     layer(rglru(128, 2, 3), moe(6, 6, 64, 1.0, shared=64)),
 ])
@@ -88,8 +88,8 @@ CONFIG_M = model(101, 50, 3e-6, 0.3, [
     layer(rglru(35, 1, 2), dense(13, 100.0)),
 ], softcap=30.0)
 # N: recurrences only: the model has no pages at all, only state slots.
-CONFIG_N = model(150, 64, 1e-5, 0.5, [
-    layer(rglru(64, 2, 4), moe(4, 2, 32, 1.5, groups=(2, 1))),
+CONFIG_N = model(150, 64, 1e-5, 0.4, [
+    layer(rglru(64, 2, 4), moe(4, 2, 32, 1.25, groups=(2, 1))),
     layer(rglru(96, 3, 2), dense(64, 1.0)),
 ])
 # P: heads of 128 with values of 128 (the tcgen05 prefill attention and the decode attention with its input stage inside at
