@@ -280,12 +280,71 @@ rms_gate_kernel(const float* __restrict__ y, const TI* __restrict__ gate, int ld
     out[(size_t)t * width + i] = from_float<TI>(yr[i] * inv * w[i] * sigmoid_f(to_float(gr[i])));
 }
 
+// Four elements a thread and access; up to kGateKeep vectors of y stay in registers between the sum and the write, so a
+// row is read once.
+constexpr int kGateKeep = 4;
+
+__global__ void __launch_bounds__(256)
+rms_gate_vec_kernel(const float* __restrict__ y, const __nv_bfloat16* __restrict__ gate, int ld_gate, const float* __restrict__ w,
+                    __nv_bfloat16* __restrict__ out, int width, float eps, float scale) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  __shared__ float scratch[33];
+  const int t = blockIdx.x, n4 = width / 4;
+  const float4* yr = reinterpret_cast<const float4*>(y + (size_t)t * width);
+  const uint2* gr = reinterpret_cast<const uint2*>(gate + (size_t)t * ld_gate);
+  const float4* wr = reinterpret_cast<const float4*>(w);
+  uint2* o = reinterpret_cast<uint2*>(out + (size_t)t * width);
+  float4 keep[kGateKeep];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < kGateKeep; ++j) {
+    const int i = threadIdx.x + j * blockDim.x;
+    if (i < n4) {
+      keep[j] = yr[i];
+      ss = fmaf(keep[j].x, keep[j].x, ss); ss = fmaf(keep[j].y, keep[j].y, ss);
+      ss = fmaf(keep[j].z, keep[j].z, ss); ss = fmaf(keep[j].w, keep[j].w, ss);
+    }
+  }
+  for (int i = threadIdx.x + kGateKeep * blockDim.x; i < n4; i += blockDim.x) {
+    const float4 v = yr[i];
+    ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = scale / sqrtf(ss / (float)width + eps);
+  auto write = [&](int i, const float4 v) {
+    const uint2 g = gr[i];
+    const float4 wv = wr[i];
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * inv * wv.x * sigmoid_f(__uint_as_float(g.x << 16)),
+                                                    v.y * inv * wv.y * sigmoid_f(__uint_as_float(g.x & 0xFFFF0000u)));
+    const __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * inv * wv.z * sigmoid_f(__uint_as_float(g.y << 16)),
+                                                    v.w * inv * wv.w * sigmoid_f(__uint_as_float(g.y & 0xFFFF0000u)));
+    uint2 pk;
+    pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+    pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+    o[i] = pk;
+  };
+#pragma unroll
+  for (int j = 0; j < kGateKeep; ++j) {
+    const int i = threadIdx.x + j * blockDim.x;
+    if (i < n4) write(i, keep[j]);
+  }
+  for (int i = threadIdx.x + kGateKeep * blockDim.x; i < n4; i += blockDim.x) write(i, yr[i]);
+}
+
 // y: [rows, width] 32-bit; gate: [rows, ld_gate] of `dtype` (its first `width` columns from the pointer given);
 // out: [rows, width] of `dtype`.
 ILB_EXPORT int ilb_rms_gate(const float* y, const void* gate, int dtype, int ld_gate, const float* w, void* out, int rows,
                             int width, float eps, float scale, cudaStream_t stream) {
   ILB_REQUIRE(rows >= 0 && width > 0 && ld_gate >= width && eps > 0.f, "rms_gate: bad sizes");
   if (rows == 0) return 0;
+  if (dtype == kBF16 && width % 4 == 0 && ld_gate % 4 == 0 && ((uintptr_t)y % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
+      ((uintptr_t)gate % 8 == 0) && ((uintptr_t)out % 8 == 0)) {
+    const int per = width / 4, vthreads = per >= 1024 ? 256 : (per >= 256 ? 128 : 64);
+    ilb::launch(rms_gate_vec_kernel, dim3(rows), dim3(vthreads), 0, stream, y, (const __nv_bfloat16*)gate, ld_gate, w, (__nv_bfloat16*)out, width,
+                eps, scale);
+    return check_launch("rms_gate");
+  }
   const int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : 64);
   if (dtype == kF32)
     ilb::launch(rms_gate_kernel<float>, dim3(rows), dim3(threads), 0, stream, y, (const float*)gate, ld_gate, w, (float*)out, width, eps, scale);

@@ -468,6 +468,26 @@ def test_linear_attention_with_a_constant_decay(heads, d, dv, decay):
         assert float(state[1].min()) == 5.0
 
 
+@pytest.mark.parametrize("width,pad", [(18, 3), (64, 4), (1024, 8), (5000, 0), (4100, 2)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_over_whole_rows_with_a_sigmoid_gate(width, pad, dtype):
+    """Rows on 16-byte boundaries (four elements an access, a row read once up to 4,096 elements, longer rows read twice) and
+    others; the gate's columns lie behind other columns of a wider matrix."""
+    from inferloop_b200.csrc import ops
+    g = torch.Generator().manual_seed(width + pad)
+    T = 11
+    y = 3 * torch.randn(T, width, generator=g)
+    z = (2 * torch.randn(T, 8 + width + pad, generator=g)).to(dtype)
+    w = 1 + 0.2 * torch.randn(width, generator=g)
+    out = torch.empty(T, width, dtype=dtype, device=DEV)
+    ops.rms_gate(f32(y), z.to(DEV)[:, 8:], f32(w), 1e-5, out, 0.75)
+    ref = plain.rms(y.double(), 1e-5) * w.double() * torch.sigmoid(z.double()[:, 8:8 + width]) * 0.75
+    if dtype == torch.float32:
+        assert_close(out, ref, "float32", "norm and gate")
+    else:
+        assert (out.double().cpu() - ref).abs().max() <= 2.0 ** -8 * ref.abs().max()
+
+
 @pytest.mark.parametrize("width,extra", [(24, 8), (30, 3), (256, 64), (1000, 24)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_silu_of_a_projections_leading_columns(width, extra, dtype):
