@@ -445,25 +445,27 @@ def silu_rows(x: torch.Tensor, width: int, out: torch.Tensor) -> None:
 
 def rms_gate(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, scale: float = 1.0) -> None:
     """out = y / sqrt(mean(y^2) + eps) * weight * sigmoid(gate) * scale over whole rows; y 32-bit, gate [T, >= width]
-    (its first `width` columns) and out in the compute dtype."""
+    (its first `width` columns) and out [T, width] (rows of any stride) in the compute dtype."""
     _need(y, "rms_gate y", torch.float32); _need(gate, "rms_gate gate", contiguous=False); _need(weight, "rms_gate weight", torch.float32)
-    _need(out, "rms_gate out", gate.dtype)
+    _need(out, "rms_gate out", gate.dtype, contiguous=False)
     T, width = y.shape
-    if gate.shape[0] != T or gate.shape[1] < width or gate.stride(1) != 1 or weight.numel() != width or out.shape != y.shape:
+    if gate.shape[0] != T or gate.shape[1] < width or gate.stride(1) != 1 or weight.numel() != width or out.shape != y.shape \
+            or out.stride(1) != 1:
         raise KernelError("rms_gate: shapes do not agree")
-    _call("recurrent", "ilb_rms_gate", _ptr(y), _ptr(gate), _i(_code(gate)), _i(gate.stride(0)), _ptr(weight), _ptr(out), _i(T), _i(width),
-          _f(eps), _f(scale), _stream(out))
+    _call("recurrent", "ilb_rms_gate", _ptr(y), _ptr(gate), _i(_code(gate)), _i(gate.stride(0)), _ptr(weight), _ptr(out), _i(out.stride(0)),
+          _i(T), _i(width), _f(eps), _f(scale), _stream(out))
 
 
-def head_gate(o: torch.Tensor, gate: torch.Tensor, heads: int, scale: float = 1.0) -> None:
-    """o[t, h, :] *= sigmoid(gate[t, h]) * scale in place; o [T, heads * dv], gate [T, >= heads] (its first `heads`
-    columns), both in the compute dtype."""
-    _need(o, "head_gate o"); _need(gate, "head_gate gate", o.dtype, contiguous=False)
+def head_gate(o: torch.Tensor, gate: torch.Tensor, heads: int, scale: float = 1.0, out: Optional[torch.Tensor] = None) -> None:
+    """out[t, h, :] = o[t, h, :] * sigmoid(gate[t, h]) * scale; o [T, heads * dv], gate [T, >= heads] (its first `heads`
+    columns), out [T, heads * dv] with rows of any stride (default: o itself, in place), all in the compute dtype."""
+    _need(o, "head_gate o"); _need(gate, "head_gate gate", o.dtype, contiguous=False); _need(out, "head_gate out", o.dtype, contiguous=False)
     T, width = o.shape
-    if width % heads or gate.shape[0] != T or gate.shape[1] < heads or gate.stride(1) != 1:
+    dst = o if out is None else out
+    if width % heads or gate.shape[0] != T or gate.shape[1] < heads or gate.stride(1) != 1 or dst.shape != o.shape or dst.stride(1) != 1:
         raise KernelError("head_gate: shapes do not agree")
-    _call("recurrent", "ilb_head_gate", _ptr(o), _ptr(gate), _i(_code(o)), _i(gate.stride(0)), _i(T), _i(heads), _i(width // heads),
-          _f(scale), _stream(o))
+    _call("recurrent", "ilb_head_gate", _ptr(o), _ptr(dst), _i(dst.stride(0)), _ptr(gate), _i(_code(o)), _i(gate.stride(0)), _i(T), _i(heads),
+          _i(width // heads), _f(scale), _stream(o))
 
 
 def gated_rows(a: torch.Tensor, table: torch.Tensor, col0: int, tokens: torch.Tensor, out: torch.Tensor) -> None:

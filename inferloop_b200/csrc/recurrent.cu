@@ -13,7 +13,8 @@
 //   silu_rows   out = silu(x) of the leading columns of a projection, widened to 32-bit: the inputs of a linear
 //               attention whose queries, keys and values pass silu.
 //   rms_gate    out = y / sqrt(mean(y^2) + eps) * w * sigmoid(gate) * scale over a whole row.
-//   head_gate   o[t, h, :] *= sigmoid(g[t, h]) * scale: one gate a head on an attention's output.
+//   head_gate   dst[t, h, :] = o[t, h, :] * sigmoid(g[t, h]) * scale: one gate a head on an attention's output (in place, or into
+//               the columns of a wider matrix).
 //
 // All arithmetic is 32-bit; the compute dtype is the storage type of the projections that come in and of the rows
 // that go to the next product.  A sequence whose slot is negative (a dummy row that pads a recorded launch) starts
@@ -265,7 +266,7 @@ ILB_EXPORT int ilb_silu_rows(const void* x, int dtype, int ld, float* out, int r
 template <typename TI>
 __global__ void __launch_bounds__(256)
 rms_gate_kernel(const float* __restrict__ y, const TI* __restrict__ gate, int ld_gate, const float* __restrict__ w,
-                TI* __restrict__ out, int width, float eps, float scale) {
+                TI* __restrict__ out, int ld_out, int width, float eps, float scale) {
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();
   __shared__ float scratch[33];
@@ -277,7 +278,7 @@ rms_gate_kernel(const float* __restrict__ y, const TI* __restrict__ gate, int ld
   ss = block_sum(ss, scratch);
   const float inv = scale / sqrtf(ss / (float)width + eps);
   for (int i = threadIdx.x; i < width; i += blockDim.x)
-    out[(size_t)t * width + i] = from_float<TI>(yr[i] * inv * w[i] * sigmoid_f(to_float(gr[i])));
+    out[(size_t)t * ld_out + i] = from_float<TI>(yr[i] * inv * w[i] * sigmoid_f(to_float(gr[i])));
 }
 
 // Four elements a thread and access; up to kGateKeep vectors of y stay in registers between the sum and the write, so a
@@ -286,7 +287,7 @@ constexpr int kGateKeep = 4;
 
 __global__ void __launch_bounds__(256)
 rms_gate_vec_kernel(const float* __restrict__ y, const __nv_bfloat16* __restrict__ gate, int ld_gate, const float* __restrict__ w,
-                    __nv_bfloat16* __restrict__ out, int width, float eps, float scale) {
+                    __nv_bfloat16* __restrict__ out, int ld_out, int width, float eps, float scale) {
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();
   __shared__ float scratch[33];
@@ -294,7 +295,7 @@ rms_gate_vec_kernel(const float* __restrict__ y, const __nv_bfloat16* __restrict
   const float4* yr = reinterpret_cast<const float4*>(y + (size_t)t * width);
   const uint2* gr = reinterpret_cast<const uint2*>(gate + (size_t)t * ld_gate);
   const float4* wr = reinterpret_cast<const float4*>(w);
-  uint2* o = reinterpret_cast<uint2*>(out + (size_t)t * width);
+  uint2* o = reinterpret_cast<uint2*>(out + (size_t)t * ld_out);
   float4 keep[kGateKeep];
   float ss = 0.f;
 #pragma unroll
@@ -333,24 +334,24 @@ rms_gate_vec_kernel(const float* __restrict__ y, const __nv_bfloat16* __restrict
 }
 
 // y: [rows, width] 32-bit; gate: [rows, ld_gate] of `dtype` (its first `width` columns from the pointer given);
-// out: [rows, width] of `dtype`.
-ILB_EXPORT int ilb_rms_gate(const float* y, const void* gate, int dtype, int ld_gate, const float* w, void* out, int rows,
+// out: [rows, ld_out] of `dtype` (its first `width` columns).
+ILB_EXPORT int ilb_rms_gate(const float* y, const void* gate, int dtype, int ld_gate, const float* w, void* out, int ld_out, int rows,
                             int width, float eps, float scale, cudaStream_t stream) {
-  ILB_REQUIRE(rows >= 0 && width > 0 && ld_gate >= width && eps > 0.f, "rms_gate: bad sizes");
+  ILB_REQUIRE(rows >= 0 && width > 0 && ld_gate >= width && ld_out >= width && eps > 0.f, "rms_gate: bad sizes");
   if (rows == 0) return 0;
-  if (dtype == kBF16 && width % 4 == 0 && ld_gate % 4 == 0 && ((uintptr_t)y % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
+  if (dtype == kBF16 && width % 4 == 0 && ld_gate % 4 == 0 && ld_out % 4 == 0 && ((uintptr_t)y % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
       ((uintptr_t)gate % 8 == 0) && ((uintptr_t)out % 8 == 0)) {
     const int per = width / 4, vthreads = per >= 1024 ? 256 : (per >= 256 ? 128 : 64);
-    ilb::launch(rms_gate_vec_kernel, dim3(rows), dim3(vthreads), 0, stream, y, (const __nv_bfloat16*)gate, ld_gate, w, (__nv_bfloat16*)out, width,
-                eps, scale);
+    ilb::launch(rms_gate_vec_kernel, dim3(rows), dim3(vthreads), 0, stream, y, (const __nv_bfloat16*)gate, ld_gate, w, (__nv_bfloat16*)out, ld_out,
+                width, eps, scale);
     return check_launch("rms_gate");
   }
   const int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : 64);
   if (dtype == kF32)
-    ilb::launch(rms_gate_kernel<float>, dim3(rows), dim3(threads), 0, stream, y, (const float*)gate, ld_gate, w, (float*)out, width, eps, scale);
+    ilb::launch(rms_gate_kernel<float>, dim3(rows), dim3(threads), 0, stream, y, (const float*)gate, ld_gate, w, (float*)out, ld_out, width, eps, scale);
   else if (dtype == kBF16)
     ilb::launch(rms_gate_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, stream, y, (const __nv_bfloat16*)gate, ld_gate, w,
-                (__nv_bfloat16*)out, width, eps, scale);
+                (__nv_bfloat16*)out, ld_out, width, eps, scale);
   else return fail("rms_gate: unknown dtype %d", dtype);
   return check_launch("rms_gate");
 }
@@ -358,21 +359,21 @@ ILB_EXPORT int ilb_rms_gate(const float* y, const void* gate, int dtype, int ld_
 // ---------------------------------------------------------------- one gate a head
 template <typename TI>
 __global__ void __launch_bounds__(256)
-head_gate_kernel(TI* __restrict__ o, const TI* __restrict__ gate, int ld_gate, int rows, int heads, int dv, float scale) {
+head_gate_kernel(const TI* o, TI* dst, int ld_dst, const TI* __restrict__ gate, int ld_gate, int rows, int heads, int dv, float scale) {
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();
   const size_t width = (size_t)heads * dv, n = (size_t)rows * width;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-    const size_t r = i / width;
-    const int h = (int)((i % width) / dv);
-    o[i] = from_float<TI>(to_float(o[i]) * (sigmoid_f(to_float(gate[r * ld_gate + h])) * scale));
+    const size_t r = i / width, c = i % width;
+    const int h = (int)(c / dv);
+    dst[r * ld_dst + c] = from_float<TI>(to_float(o[i]) * (sigmoid_f(to_float(gate[r * ld_gate + h])) * scale));
   }
 }
 
 // Eight bfloat16 elements of one head a thread and access.
 __global__ void __launch_bounds__(256)
-head_gate_vec_kernel(__nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ gate, int ld_gate, int rows, int heads, int dv8,
-                     float scale) {
+head_gate_vec_kernel(const __nv_bfloat16* o, __nv_bfloat16* dst, int ld_dst, const __nv_bfloat16* __restrict__ gate, int ld_gate, int rows,
+                     int heads, int dv8, float scale) {
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();
   const int per_row = heads * dv8;
@@ -388,28 +389,28 @@ head_gate_vec_kernel(__nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restr
       const __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(w[j] << 16) * g, __uint_as_float(w[j] & 0xFFFF0000u) * g);
       w[j] = *reinterpret_cast<const uint32_t*>(&p);
     }
-    *reinterpret_cast<uint4*>(o + i * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+    *reinterpret_cast<uint4*>(dst + r * ld_dst + (i % per_row) * 8) = make_uint4(w[0], w[1], w[2], w[3]);
   }
 }
 
-// o: [rows, heads * dv] of `dtype`, in place; gate: [rows, ld_gate] of `dtype`, head h's logit at column h of the
-// pointer given.
-ILB_EXPORT int ilb_head_gate(void* o, const void* gate, int dtype, int ld_gate, int rows, int heads, int dv, float scale,
-                             cudaStream_t stream) {
-  ILB_REQUIRE(rows >= 0 && heads > 0 && dv > 0 && ld_gate >= heads, "head_gate: bad sizes");
+// o: [rows, heads * dv] of `dtype`; dst: [rows, ld_dst] of `dtype` (its first heads * dv columns; it may be o itself);
+// gate: [rows, ld_gate] of `dtype`, head h's logit at column h of the pointer given.
+ILB_EXPORT int ilb_head_gate(const void* o, void* dst, int ld_dst, const void* gate, int dtype, int ld_gate, int rows, int heads, int dv,
+                             float scale, cudaStream_t stream) {
+  ILB_REQUIRE(rows >= 0 && heads > 0 && dv > 0 && ld_gate >= heads && ld_dst >= heads * dv, "head_gate: bad sizes");
   if (rows == 0) return 0;
   const size_t n = (size_t)rows * heads * dv;
-  if (dtype == kBF16 && dv % 8 == 0 && ((uintptr_t)o % 16 == 0)) {
+  if (dtype == kBF16 && dv % 8 == 0 && ld_dst % 8 == 0 && ((uintptr_t)o % 16 == 0) && ((uintptr_t)dst % 16 == 0)) {
     const size_t n8 = n / 8;
     const int blocks8 = (int)((n8 + 255) / 256 < 148 * 16 ? (n8 + 255) / 256 : 148 * 16);
-    ilb::launch(head_gate_vec_kernel, dim3(blocks8), dim3(256), 0, stream, (__nv_bfloat16*)o, (const __nv_bfloat16*)gate, ld_gate, rows, heads,
-                dv / 8, scale);
+    ilb::launch(head_gate_vec_kernel, dim3(blocks8), dim3(256), 0, stream, (const __nv_bfloat16*)o, (__nv_bfloat16*)dst, ld_dst, (const __nv_bfloat16*)gate,
+                ld_gate, rows, heads, dv / 8, scale);
     return check_launch("head_gate");
   }
   const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
-  if (dtype == kF32) ilb::launch(head_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)o, (const float*)gate, ld_gate, rows, heads, dv, scale);
+  if (dtype == kF32) ilb::launch(head_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)o, (float*)dst, ld_dst, (const float*)gate, ld_gate, rows, heads, dv, scale);
   else if (dtype == kBF16)
-    ilb::launch(head_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)o, (const __nv_bfloat16*)gate, ld_gate,
+    ilb::launch(head_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)o, (__nv_bfloat16*)dst, ld_dst, (const __nv_bfloat16*)gate, ld_gate,
                 rows, heads, dv, scale);
   else return fail("head_gate: unknown dtype %d", dtype);
   return check_launch("head_gate");

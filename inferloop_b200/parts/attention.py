@@ -201,8 +201,16 @@ class GQAttention(Mixer):
         linear(x, self.w_qkv, qkv, self.b_qkv)
         self.forward_projected(qkv, residual, step, cache)
 
-    def forward_projected(self, qkv: torch.Tensor, residual: torch.Tensor, step, cache) -> None:
-        """The mixer from its projection's output on: `qkv` [T, q | k | v (| gates)], rows of any stride."""
+    def output_rows(self):
+        """(matrix [hidden, heads * v_head_dim], bias or None) of the product this mixer ends with, or None when its input
+        cannot be written elsewhere (no gate kernel in between): a mixer that runs beside others can have its columns
+        stacked with theirs (`forward_projected(..., out=...)`)."""
+        return (self.w_o, self.b_o) if self.output_gate else None
+
+    def forward_projected(self, qkv: torch.Tensor, residual: torch.Tensor, step, cache, out: Optional[torch.Tensor] = None) -> None:
+        """The mixer from its projection's output on: `qkv` [T, q | k | v (| gates)], rows of any stride.  With `out`
+        [T, heads * v_head_dim] (rows of any stride) the gated attention output goes there and the output product is left to
+        the caller."""
         T = qkv.shape[0]
         ws, dt = self.ctx.workspace, self.ctx.dtype
         gate_col0 = (self.nq + self.nkv) * self.d + self.nkv * self.dv      # the heads' gate logits ride behind q | k | v
@@ -229,9 +237,7 @@ class GQAttention(Mixer):
                                        rotary_dim=self.rotary_dim or None, v_first=v_first,
                                        v_lambda=self.v_lambda if self.value_mix == "mixed" else None,
                                        v_keep=self.value_mix == "first")
-            self._gate(o, qkv, gate_col0)
-            ops.scope("attention.o_projection")
-            linear(o, self.w_o, residual, self.b_o, accumulate=True)
+            self._finish(o, qkv, gate_col0, residual, out)
             return
         q = ws.buffer("attn.q", (T, self.nq * self.d), dt)
         ops.scope("attention.qk_norm_rotation_cache_write")
@@ -251,17 +257,19 @@ class GQAttention(Mixer):
         else:
             ops.attention(q, o, cache.k, cache.v, step, table, self.window or 0, self.scale,
                           self.nq, self.nkv, self.d, workspace=ws, decode_chunk=self.decode_chunk, dv=self.dv, sink=self.sink)
-        self._gate(o, qkv, gate_col0)
-        ops.scope("attention.o_projection")
-        linear(o, self.w_o, residual, self.b_o, accumulate=True)
+        self._finish(o, qkv, gate_col0, residual, out)
 
-    def _gate(self, o: torch.Tensor, qkv: torch.Tensor, gate_col0: int) -> None:
-        """The gate a head and the mixer's constant, on what the output projection reads."""
+    def _finish(self, o: torch.Tensor, qkv: torch.Tensor, gate_col0: int, residual: torch.Tensor, out: Optional[torch.Tensor]) -> None:
+        """The gate a head and the mixer's constant on what the output product reads, then that product (or, with `out`,
+        the gated rows into the caller's matrix)."""
         if self.output_gate:
             ops.scope("attention.output_gate")
-            ops.head_gate(o, qkv[:, gate_col0:], self.nq, self.out_scale)
-        elif self.out_scale != 1.0:
-            raise ops.KernelError("attention: a constant on the output needs the gate's kernel (output_gate)")
+            ops.head_gate(o, qkv[:, gate_col0:], self.nq, self.out_scale, out=out)
+        elif out is not None:
+            raise ops.KernelError("attention: without a gate the output product is the mixer's own")
+        if out is None:
+            ops.scope("attention.o_projection")
+            linear(o, self.w_o, residual, self.b_o, accumulate=True)
 
 
 registry.register("mixer", "gqa_attention", GQAttention)

@@ -180,8 +180,13 @@ class DecayedLinearAttention(Mixer):
         linear(x, self.w_in, proj)
         self.forward_projected(proj, residual, step, cache)
 
-    def forward_projected(self, proj: torch.Tensor, residual: torch.Tensor, step, cache) -> None:
-        """The mixer from its projection's output on: `proj` [T, v | k | q | gate], rows of any stride."""
+    def output_rows(self):
+        """(matrix [hidden, heads * v_head_dim], bias or None) of the product this mixer ends with."""
+        return self.w_o, None
+
+    def forward_projected(self, proj: torch.Tensor, residual: torch.Tensor, step, cache, out=None) -> None:
+        """The mixer from its projection's output on: `proj` [T, v | k | q | gate], rows of any stride.  With `out`
+        [T, heads * v_head_dim] (rows of any stride) the normed, gated rows go there and the output product is left to the caller."""
         T, ws, dt = proj.shape[0], self.ctx.workspace, self.ctx.dtype
         ops.scope("linear_attention.activation")
         act = ws.buffer("linattn.act", (T, self.channels), torch.float32)
@@ -191,17 +196,21 @@ class DecayedLinearAttention(Mixer):
         ops.ssm_scan(act, None, 0, None, self.decays, None, cache.state["state"], y, step, self.heads, self.dv, self.d, self.heads,
                      workspace=ws, fixed_decay=True)
         ops.scope("linear_attention.norm_gate")
-        gated = ws.buffer("linattn.gated", (T, self.inner), dt)
+        gated = out if out is not None else ws.buffer("linattn.gated", (T, self.inner), dt)
         ops.rms_gate(y, proj[:, self.channels:], self.norm_w, self.eps, gated, self.out_scale)
-        ops.scope("linear_attention.out_projection")
-        linear(gated, self.w_o, residual, accumulate=True)
+        if out is None:
+            ops.scope("linear_attention.out_projection")
+            linear(gated, self.w_o, residual, accumulate=True)
 
 
 class ParallelMixers(Mixer):
     """spec: `branches` = ((sub-prefix, PartSpec of role mixer), ...).  Every branch reads the block's input and adds
     into the block's output; a branch's constant on its output is its own parameter (`out_scale`).  Branches that start
     with one product of the input each (`input_rows` / `forward_projected`) share ONE product: their matrices are
-    stacked at load (each branch keeps a view of its rows) and every branch reads its columns of the result."""
+    stacked at load (each branch keeps a view of its rows) and every branch reads its columns of the result.  Branches
+    that also end with one product each (`output_rows`) share that too: every branch writes what its product would read
+    into its columns of one matrix, and one product with the branches' matrices side by side adds all of them into the
+    block's output (the sum over a row of the stacked matrix is the sum of the branches' products)."""
 
     def __init__(self, spec, ctx, prefix: str = "") -> None:
         super().__init__(spec, ctx, prefix)
@@ -209,8 +218,8 @@ class ParallelMixers(Mixer):
         if not branches:
             raise ValueError("parallel: no branches")
         self.parts = [registry.build("mixer", part, ctx, prefix + sub) for sub, part in branches]
-        self.w_all = self.b_all = None
-        self.columns = []
+        self.w_all = self.b_all = self.w_out = self.b_out = None
+        self.columns, self.out_columns = [], []
         if sum(1 for p in self.parts if p.cache_needs().paged is not None) > 1:
             raise ValueError("parallel: at most one branch may keep keys and values in pages")
 
@@ -224,8 +233,8 @@ class ParallelMixers(Mixer):
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         for p in self.parts:
             p.bind(tensors)
-        self.w_all = self.b_all = None
-        self.columns = []
+        self.w_all = self.b_all = self.w_out = self.b_out = None
+        self.columns, self.out_columns = [], []
         if len(self.parts) < 2 or not all(hasattr(p, "input_rows") and hasattr(p, "forward_projected") for p in self.parts):
             return
         rows = [p.input_rows() for p in self.parts]
@@ -242,6 +251,16 @@ class ParallelMixers(Mixer):
             if hasattr(p, "take_input_rows"):
                 p.take_input_rows(self.w_all[at:at + w.shape[0]])
             at += w.shape[0]
+        outs = [p.output_rows() if hasattr(p, "output_rows") else None for p in self.parts]
+        if any(o is None for o in outs) or any(w.shape[1] % 8 for w, _ in outs) or len({(w.dtype, w.shape[0]) for w, _ in outs}) != 1:
+            return
+        self.w_out = torch.cat([w for w, _ in outs], dim=1).contiguous()
+        biases = [b for _, b in outs if b is not None]
+        self.b_out = torch.stack(biases).sum(0).contiguous() if biases else None
+        at = 0
+        for w, _ in outs:
+            self.out_columns.append((at, at + w.shape[1]))
+            at += w.shape[1]
 
     def cache_needs(self) -> CacheNeeds:
         paged, slots = None, []
@@ -252,7 +271,7 @@ class ParallelMixers(Mixer):
         return CacheNeeds(paged=paged, slots=tuple(slots))
 
     def scratch_bytes(self, tokens: int) -> int:
-        return sum(p.scratch_bytes(tokens) for p in self.parts)          # (the shared result is the branches' own, side by side)
+        return sum(p.scratch_bytes(tokens) for p in self.parts)          # (the shared matrices are the branches' own, side by side)
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor, step, cache) -> None:
         proj = None
@@ -260,14 +279,23 @@ class ParallelMixers(Mixer):
             proj = self.ctx.workspace.buffer("parallel.proj", (x.shape[0], self.w_all.shape[0]), self.ctx.dtype)
             ops.scope("parallel.in_projection")
             linear(x, self.w_all, proj, self.b_all)
+        pre = None
+        if self.w_out is not None:
+            pre = self.ctx.workspace.buffer("parallel.pre", (x.shape[0], self.w_out.shape[1]), self.ctx.dtype)
         for i, p in enumerate(self.parts):
             tag = f"{i}."
             own = dataclasses.replace(cache, state={k[len(tag):]: v for k, v in cache.state.items() if k.startswith(tag)})
-            if proj is not None:
+            if pre is not None:
+                (a, b), (c, d) = self.columns[i], self.out_columns[i]
+                p.forward_projected(proj[:, a:b], residual, step, own, out=pre[:, c:d])
+            elif proj is not None:
                 a, b = self.columns[i]
                 p.forward_projected(proj[:, a:b], residual, step, own)
             else:
                 p.forward(x, residual, step, own)
+        if pre is not None:
+            ops.scope("parallel.out_projection")
+            linear(pre, self.w_out, residual, self.b_out, accumulate=True)
 
 
 registry.register("mixer", "gated_linear_recurrence", GatedLinearRecurrence)
